@@ -88,13 +88,13 @@ class CacheGroup:
     owners: List[int]                      # schedule indices whose runs own a cache layer here
     page_size: int
     pool: PagePool
-    tensor: Optional[torch.Tensor] = None  # [n_layers, n_pages, 2, n_kv_head, page_size, head_dim]
+    tensor: Optional[torch.Tensor] = None  # [n_layers, n_pages, planes, n_kv_head, page_size, head_dim]
 
     def layer_of(self, schedule_index: int) -> int:
         return self.owners.index(schedule_index)
 
     def bytes_per_page(self, itemsize: int) -> int:
-        return len(self.owners) * 2 * self.spec.n_kv_head * self.page_size * self.spec.head_dim * itemsize
+        return len(self.owners) * self.spec.planes * self.spec.n_kv_head * self.page_size * self.spec.head_dim * itemsize
 
 
 @dataclass
@@ -191,7 +191,7 @@ class CacheManager:
             group = CacheGroup(spec, owners, self.page_size, PagePool(n_pages))
             if device is not None:
                 group.tensor = torch.zeros(
-                    (len(owners), n_pages + (1 if padding else 0), 2, spec.n_kv_head, self.page_size, spec.head_dim),
+                    (len(owners), n_pages + (1 if padding else 0), spec.planes, spec.n_kv_head, self.page_size, spec.head_dim),
                     dtype=dtype, device=device)
             self.groups.append(group)
         self._group_of: Dict[int, int] = {idx: gi for gi, g in enumerate(self.groups) for idx in g.owners}

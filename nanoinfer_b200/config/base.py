@@ -130,7 +130,13 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
 
 
 def architecture_name(raw: Dict[str, Any]) -> str:
+    """The name a config.json gives its architecture: the first of ``architectures`` (a list), or
+    ``architecture`` (one name)."""
+    one = raw.get("architecture")
+    if "architectures" not in raw and isinstance(one, str) and one:
+        return one
     archs = raw.get("architectures")
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' one name)")
     return archs[0]

@@ -133,6 +133,54 @@ int nib_sample(const float* logits, int ld, int n_rows, int V, const int* row_sl
                const float* temperature, const int* top_k, unsigned long long* rng_state, int* out,
                int* last_token, unsigned long long* scratch, int teams, cudaStream_t stream);
 
+// ---- layers that normalise after the sum, and a weighted average over the layers' results (stream_norm.cu)
+// out[r] = x[rows[r]] / sqrt(mean(x^2) + eps) * w (rows null: x[r]).
+int nib_rmsnorm(int out_dtype, const float* x, const int* rows, const float* w, void* out, int n_rows, int C,
+                float eps, cudaStream_t stream);
+// xn = cast(x); level0 = x (may be null); x = alpha * x.
+int nib_stream_enter(int out_dtype, float* x, void* xn, float* level0, float alpha, int n_rows, int C,
+                     cudaStream_t stream);
+// y = rmsnorm(x) * w; with levels [n_levels][level_stride]: levels[n_levels - 1] = y and z = sum_j mix[j] *
+// levels[j], else z = y; xn = cast(z) (may be null); x = alpha_next * z.
+int nib_post_norm(int out_dtype, float* x, const float* w, float eps, float* levels, long long level_stride,
+                  int n_levels, const float* mix, void* xn, float alpha_next, int n_rows, int C,
+                  cudaStream_t stream);
+// kind 1: tanh; kind 2: xIELU with prm = {p, q} on the device.  in and out may be the same buffer.
+int nib_unary(int in_dtype, int out_dtype, const void* in, int ld_in, void* out, int ld_out, int n_rows,
+              int n_cols, int kind, const float* prm, cudaStream_t stream);
+
+// ---- attention through a shared low-rank latent (latent_attention.cu)
+int nib_latent_prep(int dtype, const float* proj, int ld, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                    const double* freqs, const float* wq, const float* wkv, float eps, void* cq, int ld_cq,
+                    void* cache, const int* block_table, int max_blocks, const int* row_entry,
+                    const int* positions, int T, int page_size, int n_pages, int has_kv, int* status,
+                    cudaStream_t stream);
+int nib_rope_heads(int dtype, const void* q, int ldq, int nope, int rot_dim, int rot_dims, const double* freqs,
+                   const int* positions, float* out, int out_dim, int out_off, int n_head, int T,
+                   cudaStream_t stream);
+int nib_latent_attention(int dtype, const float* q, const void* cache, void* out, int ldo, const int* block_table,
+                         int max_blocks, const int* rows, const int* row_entry, const int* positions, int n_rows,
+                         int n_head, int kv_rank, int D, int page_size, int n_pages, float scale, int window,
+                         int* status, cudaStream_t stream);
+
+// ---- a product per head (linear_heads.cu): out[t, h, :N] = a[t, h, :K] . w[h]^T, w [n_head, N, K]
+int nib_linear_heads(int dtype, int out_dtype, const void* a, int lda, int a_head_stride, const void* w, void* out,
+                     int ldo, int out_head_stride, int M, int n_head, int N, int K, cudaStream_t stream);
+
+// ---- the generalised delta rule (delta_rule.cu)
+int nib_delta_rule(int dtype, const float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off,
+                   const float* wl, int ld_w, const float* w0, const float* a_bias, const float* norm_w,
+                   float* state, const int* entry_start, const int* entry_slot, int n_entries, int n_head, int dim,
+                   float eps, void* out, int ldo, cudaStream_t stream);
+
+// ---- a routed feed-forward (moe.cu)
+int nib_moe_route(int dtype, const void* h, int ldh, const void* w_router, int T, int C, int n_expert, int top,
+                  int renorm, int* ids, float* weights, cudaStream_t stream);
+int nib_moe_up(int dtype, const void* h, int ldh, const void* w_up, const int* ids, void* inner, int T, int C,
+               int F, int top, int act, cudaStream_t stream);
+int nib_moe_down(int dtype, const void* inner, const void* w_down, const int* ids, const float* weights, float* x,
+                 int T, int C, int F, int top, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

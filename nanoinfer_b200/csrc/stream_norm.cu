@@ -1,0 +1,191 @@
+// Kernels on the 32-bit residual stream for layers that normalise AFTER the sum:
+//   x <- norm(alpha * x + sublayer(x))
+// and for models that hand each layer a weighted average of all earlier layers' results.
+//
+// The stream is kept pre-scaled: a sublayer's last product adds into alpha * x, which the kernel
+// before it has left in place together with the sublayer's input (x itself, in the engine's dtype).
+//   stream_enter : xn = cast(x); level0 = x (optional); x = alpha * x
+//   post_norm    : y = x / sqrt(mean(x^2) + eps) * w;
+//                  with levels: level[n-1] = y; z = sum_j mix[j] * level[j]   (j ascending), else z = y;
+//                  xn = cast(z) (optional); x = alpha_next * z
+//   rmsnorm      : out[r] = x[rows[r]] / sqrt(mean + eps) * w   (the model's last norm, wanted rows only)
+//   act          : tanh, or xIELU with its two numbers p, q read from the device:
+//                  z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2
+// Statistics, sums and the activation's arithmetic are 32-bit.
+#include "api.h"
+#include "common.cuh"
+
+namespace nib {
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const float* x, const int* __restrict__ rows, const float* __restrict__ w, OutT* out, int C,
+               float eps) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ float smem[];
+  float* row = smem;
+  float* scratch = smem + C;
+  const int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * C;
+  float q = 0.0f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float v = src[c];
+    row[c] = v;
+    q += v * v;
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(q, scratch) / (float)C + eps);
+  OutT* o = out + (size_t)r * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) o[c] = from_float<OutT>(row[c] * rstd * w[c]);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+stream_enter_kernel(float* x, OutT* xn, float* level0, float alpha, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = x[i];
+  xn[i] = from_float<OutT>(v);
+  if (level0 != nullptr) level0[i] = v;
+  x[i] = alpha * v;
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+post_norm_kernel(float* x, const float* __restrict__ w, float eps, float* levels, long long level_stride,
+                 int n_levels, const float* __restrict__ mix, OutT* xn, float alpha_next, int C) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ float smem[];
+  float* row = smem;
+  float* scratch = smem + C;
+  const size_t base = (size_t)blockIdx.x * C;
+  float q = 0.0f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float v = x[base + c];
+    row[c] = v;
+    q += v * v;
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(q, scratch) / (float)C + eps);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float y = row[c] * rstd * w[c];
+    float z = y;
+    if (levels != nullptr) {
+      levels[(size_t)(n_levels - 1) * level_stride + base + c] = y;
+      z = 0.0f;
+      for (int j = 0; j + 1 < n_levels; ++j) z += mix[j] * levels[(size_t)j * level_stride + base + c];
+      z += mix[n_levels - 1] * y;
+    }
+    if (xn != nullptr) xn[base + c] = from_float<OutT>(z);
+    x[base + c] = alpha_next * z;
+  }
+}
+
+enum : int { UNARY_TANH = 1, UNARY_XIELU = 2 };
+
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(256)
+unary_kernel(const InT* in, int ld_in, OutT* out, int ld_out, int n_rows, int n_cols, int kind,
+             const float* __restrict__ prm) {
+  pdl_trigger();
+  float sp = 0.0f, sq = 0.0f;
+  if (kind == UNARY_XIELU) {
+    sp = softplus_f(prm[0]);
+    sq = 0.5f + softplus_f(prm[1]);
+  }
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_rows * n_cols) return;
+  const int r = (int)(i / n_cols), c = (int)(i % n_cols);
+  const float z = to_float(in[(size_t)r * ld_in + c]);
+  float y;
+  if (kind == UNARY_TANH)
+    y = tanhf(z);
+  else
+    y = z > 0.0f ? sp * z * z + 0.5f * z : sq * (expm1f(z) - z) + 0.5f * z;
+  out[(size_t)r * ld_out + c] = from_float<OutT>(y);
+}
+
+}  // namespace nib
+
+using namespace nib;
+
+extern "C" int nib_rmsnorm(int out_dtype, const float* x, const int* rows, const float* w, void* out, int n_rows,
+                           int C, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (C <= 0 || C > 48000) return NIB_ERR_UNSUPPORTED_SIZE;
+  const size_t smem = (size_t)(C + 32) * sizeof(float);
+  const int threads = C >= 1024 ? 256 : 128;
+  if (out_dtype == DT_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, rows, w, (float*)out, C, eps);
+  } else if (out_dtype == DT_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, stream, x, rows, w, (bf16*)out, C, eps);
+  } else {
+    return NIB_ERR_BAD_ARGUMENT;
+  }
+  NIB_LAUNCH_CHECK();
+}
+
+extern "C" int nib_stream_enter(int out_dtype, float* x, void* xn, float* level0, float alpha, int n_rows, int C,
+                                cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const size_t n = (size_t)n_rows * C;
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (out_dtype == DT_F32)
+    launch_pdl(stream_enter_kernel<float>, grid, dim3(256), 0, stream, x, (float*)xn, level0, alpha, n);
+  else if (out_dtype == DT_BF16)
+    launch_pdl(stream_enter_kernel<bf16>, grid, dim3(256), 0, stream, x, (bf16*)xn, level0, alpha, n);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
+  NIB_LAUNCH_CHECK();
+}
+
+extern "C" int nib_post_norm(int out_dtype, float* x, const float* w, float eps, float* levels,
+                             long long level_stride, int n_levels, const float* mix, void* xn, float alpha_next,
+                             int n_rows, int C, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (C <= 0 || C > 48000) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (levels != nullptr && (n_levels < 1 || mix == nullptr)) return NIB_ERR_BAD_ARGUMENT;
+  const size_t smem = (size_t)(C + 32) * sizeof(float);
+  const int threads = C >= 1024 ? 256 : 128;
+  if (out_dtype == DT_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(post_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(post_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, w, eps, levels, level_stride,
+               n_levels, mix, (float*)xn, alpha_next, C);
+  } else if (out_dtype == DT_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(post_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(post_norm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, stream, x, w, eps, levels, level_stride,
+               n_levels, mix, (bf16*)xn, alpha_next, C);
+  } else {
+    return NIB_ERR_BAD_ARGUMENT;
+  }
+  NIB_LAUNCH_CHECK();
+}
+
+// kind 1: tanh; kind 2: xIELU with prm = {p, q} on the device.  in and out may be the same buffer.
+extern "C" int nib_unary(int in_dtype, int out_dtype, const void* in, int ld_in, void* out, int ld_out, int n_rows,
+                         int n_cols, int kind, const float* prm, cudaStream_t stream) {
+  if (n_rows <= 0 || n_cols <= 0) return 0;
+  if (kind != UNARY_TANH && kind != UNARY_XIELU) return NIB_ERR_BAD_ARGUMENT;
+  if (kind == UNARY_XIELU && prm == nullptr) return NIB_ERR_BAD_ARGUMENT;
+  const size_t n = (size_t)n_rows * n_cols;
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (in_dtype == DT_F32 && out_dtype == DT_F32)
+    launch_pdl(unary_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)in, ld_in, (float*)out, ld_out,
+               n_rows, n_cols, kind, prm);
+  else if (in_dtype == DT_F32 && out_dtype == DT_BF16)
+    launch_pdl(unary_kernel<float, bf16>, grid, dim3(256), 0, stream, (const float*)in, ld_in, (bf16*)out, ld_out,
+               n_rows, n_cols, kind, prm);
+  else if (in_dtype == DT_BF16 && out_dtype == DT_BF16)
+    launch_pdl(unary_kernel<bf16, bf16>, grid, dim3(256), 0, stream, (const bf16*)in, ld_in, (bf16*)out, ld_out,
+               n_rows, n_cols, kind, prm);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
+  NIB_LAUNCH_CHECK();
+}

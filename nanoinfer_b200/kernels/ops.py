@@ -16,6 +16,7 @@ from . import build as _build
 
 ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
 ACT_CODES = {None: ACT_NONE, "none": ACT_NONE, "tanh": ACT_GELU_TANH, "erf": ACT_GELU_ERF}
+UNARY_TANH, UNARY_XIELU = 1, 2
 
 STATUS_OK, STATUS_BAD_PAGE, STATUS_WAIT_TIMEOUT = 0, 1, 2
 _ERR_NAMES = {-1: "bad argument", -2: "unsupported size", -3: "CUDA driver call failed"}
@@ -71,6 +72,26 @@ _SIGNATURES = {
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
                    _c_ptr],
+    "nib_rmsnorm": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr],
+    "nib_stream_enter": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_int, _c_int, _c_ptr],
+    "nib_post_norm": [_c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, ctypes.c_longlong, _c_int, _c_ptr, _c_ptr, _c_float,
+                      _c_int, _c_int, _c_ptr],
+    "nib_unary": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "nib_latent_prep": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_float,
+                        _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                        _c_ptr, _c_ptr],
+    "nib_rope_heads": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                       _c_int, _c_int, _c_ptr],
+    "nib_latent_attention": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int,
+                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
+    "nib_linear_heads": [_c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                         _c_int, _c_int, _c_ptr],
+    "nib_delta_rule": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
+                       _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int,
+                       _c_ptr],
+    "nib_moe_route": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    "nib_moe_up": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "nib_moe_down": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
 }
 
 
@@ -848,3 +869,217 @@ def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperatur
     _check(library().nib_sample(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(row_slot),
                                 _ptr(temperature), _ptr(top_k), _ptr(rng_state), _ptr(out),
                                 _ptr(last_token), _ptr(scratch), int(bool(teams)), _stream()), "sample")
+
+
+# ------------------------------------------------------------------------------ post-norm streams
+def _f32(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.float32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous float32 tensor")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, n_rows: int,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = x[rows[r]] / sqrt(mean(x^2) + eps) * weight (rows None: x[r]); x is the 32-bit stream."""
+    C = x.shape[1]
+    _f32(x, "rmsnorm: x"); _f32(weight, "rmsnorm: weight")
+    if weight.numel() != C or out.shape[1] != C or out.shape[0] < n_rows or not out.is_contiguous():
+        raise KernelError("rmsnorm: weight [C], out contiguous [n_rows, C]")
+    if rows is not None:
+        _i32(rows, "rows")
+    if tracing():
+        _note("ln", "ln", (n_rows, C, 0), 4.0 * n_rows * C, n_rows * C * (4 + out.element_size()) + 4 * C)
+    _check(library().nib_rmsnorm(_dt(out), _ptr(x), _ptr(rows), _ptr(weight), _ptr(out), n_rows, C, float(eps),
+                                 _stream()), "rmsnorm")
+
+
+def stream_enter(x: torch.Tensor, xn: torch.Tensor, alpha: float, n_rows: int,
+                 level0: Optional[torch.Tensor] = None) -> None:
+    """xn = x in the engine's dtype, level0 = x (optional), x = alpha * x: the entry of a layer whose
+    sublayers read the stream itself and add into alpha times it."""
+    C = x.shape[1]
+    _f32(x, "stream_enter: x")
+    if xn.shape[1] != C or not xn.is_contiguous() or (level0 is not None and (level0.dtype != torch.float32
+                                                                               or not level0.is_contiguous())):
+        raise KernelError("stream_enter: xn contiguous [rows, C], level0 contiguous float32")
+    if tracing():
+        _note("other", "stream", (n_rows, C, 0), n_rows * C, n_rows * C * (8 + xn.element_size()))
+    _check(library().nib_stream_enter(_dt(xn), _ptr(x), _ptr(xn), _ptr(level0), float(alpha), n_rows, C, _stream()),
+           "stream_enter")
+
+
+def post_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, n_rows: int, xn: Optional[torch.Tensor] = None,
+              alpha_next: float = 1.0, levels: Optional[torch.Tensor] = None, n_levels: int = 0,
+              mix: Optional[torch.Tensor] = None) -> None:
+    """y = rmsnorm(x) * weight in place on the 32-bit stream.  With ``levels`` ([depth, max_rows, C], float32):
+    y becomes level ``n_levels - 1`` and the stream goes on as z = sum_j mix[j] * levels[j] over the first
+    ``n_levels``; else z = y.  ``xn`` (optional) receives z in its own dtype; x = alpha_next * z."""
+    C = x.shape[1]
+    _f32(x, "post_norm: x"); _f32(weight, "post_norm: weight")
+    stride = 0
+    if levels is not None:
+        _f32(levels, "post_norm: levels")
+        if mix is None or mix.dtype != torch.float32 or mix.numel() < n_levels or not 1 <= n_levels <= levels.shape[0] \
+                or levels.shape[2] != C or levels.shape[1] != x.shape[0]:
+            raise KernelError("post_norm: levels [depth, rows of x, C] with n_levels weights")
+        stride = levels.stride(0)
+    if xn is not None and (xn.shape[1] != C or not xn.is_contiguous()):
+        raise KernelError("post_norm: xn contiguous [rows, C]")
+    if tracing():
+        _note("ln", "ln", (n_rows, C, 0), (4.0 + 2 * n_levels) * n_rows * C,
+              n_rows * C * (8 + 4 * n_levels + (xn.element_size() if xn is not None else 0)))
+    _check(library().nib_post_norm(_dt(xn) if xn is not None else 0, _ptr(x), _ptr(weight), float(eps), _ptr(levels),
+                                   int(stride), int(n_levels), _ptr(mix), _ptr(xn), float(alpha_next), n_rows, C,
+                                   _stream()), "post_norm")
+
+
+def unary(src: torch.Tensor, out: torch.Tensor, n_rows: int, kind: int, prm: Optional[torch.Tensor] = None) -> None:
+    """out[:n_rows] = f(src[:n_rows]) element by element (``UNARY_TANH``; ``UNARY_XIELU`` with its two numbers in
+    ``prm`` on the device); src and out may be views with their own row strides, or the same buffer."""
+    if src.shape[1] != out.shape[1] or src.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("unary: src and out must have the same columns, rows contiguous")
+    if tracing():
+        _note("other", "act", (n_rows, src.shape[1], 0), 8.0 * n_rows * src.shape[1],
+              n_rows * src.shape[1] * (src.element_size() + out.element_size()))
+    _check(library().nib_unary(_dt(src), _dt(out), _ptr(src), src.stride(0), _ptr(out), out.stride(0), n_rows,
+                               src.shape[1], int(kind), _ptr(prm), _stream()), "unary")
+
+
+# ------------------------------------------------------------------------------ latent attention
+def latent_prep(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, rot_dims: int, freqs: torch.Tensor,
+                wq: torch.Tensor, wkv: Optional[torch.Tensor], eps: float, cq: torch.Tensor,
+                cache: Optional[torch.Tensor], block_table: Optional[torch.Tensor], row_entry: torch.Tensor,
+                positions: torch.Tensor, T: int, status: torch.Tensor) -> None:
+    """From the down-projections' output ``proj`` (float32 [T, q_rank (+ kv_rank + rot_dim)]): the normed query
+    latent into ``cq``, and (with ``cache``, one layer [pages, 1, 1, page_size, kv_rank + rot_dim]) the normed
+    key/value latent and the rotated shared key part into the rows' cache slots."""
+    _f32(proj, "latent_prep: proj")
+    if freqs.dtype != torch.float64 or cq.stride(1) != 1:
+        raise KernelError("latent_prep: freqs must be float64, cq rows contiguous")
+    has_kv = cache is not None
+    if has_kv:
+        n_pages, planes, heads, page_size, D = cache.shape
+        if planes != 1 or heads != 1 or D != kv_rank + rot_dim or not cache.is_contiguous() or cache.dtype != cq.dtype:
+            raise KernelError("latent_prep: cache must be contiguous [pages, 1, 1, page, kv_rank + rot_dim] of cq's dtype")
+        _i32(block_table, "block_table")
+    else:
+        n_pages = page_size = 0
+    if tracing():
+        _note("other", "latent_prep", (T, proj.shape[1], 0), 6.0 * T * proj.shape[1],
+              T * proj.shape[1] * (4 + cq.element_size()))
+    _check(library().nib_latent_prep(_dt(cq), _ptr(proj), proj.stride(0), q_rank, kv_rank, rot_dim, rot_dims,
+                                     _ptr(freqs), _ptr(wq), _ptr(wkv), float(eps), _ptr(cq), cq.stride(0),
+                                     _ptr(cache), _ptr(block_table), block_table.shape[1] if has_kv else 0,
+                                     _ptr(row_entry), _ptr(positions), T, page_size, n_pages, int(has_kv),
+                                     _ptr(status), _stream()), "latent_prep")
+
+
+def rope_heads(q: torch.Tensor, nope: int, rot_dim: int, rot_dims: int, freqs: torch.Tensor,
+               positions: torch.Tensor, out: torch.Tensor, out_off: int, n_head: int, T: int) -> None:
+    """Rotates the last ``rot_dim`` values of every head of q ([T, n_head * (nope + rot_dim)]) by the rows'
+    positions (interleaved pairs over the first ``rot_dims``) into out[t, h, out_off:], float32 [T, n_head, D]."""
+    _f32(out, "rope_heads: out")
+    if q.stride(1) != 1 or freqs.dtype != torch.float64:
+        raise KernelError("rope_heads: q rows contiguous, freqs float64")
+    if tracing():
+        _note("other", "rope", (T, n_head * rot_dim, 0), 6.0 * T * n_head * rot_dim,
+              T * n_head * rot_dim * (q.element_size() + 4))
+    _check(library().nib_rope_heads(_dt(q), _ptr(q), q.stride(0), nope, rot_dim, rot_dims, _ptr(freqs),
+                                    _ptr(positions), _ptr(out), out.shape[2], out_off, n_head, T, _stream()),
+           "rope_heads")
+
+
+def latent_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
+                     n_head: int, kv_rank: int, scale: float, window: int) -> None:
+    """Causal softmax attention of the step's rows over one latent cache layer: q float32 [T, n_head, D] (the
+    absorbed query, then the rotated part), out [T, n_head * kv_rank] the weighted sums of latents."""
+    n_pages, _, _, page_size, D = cache.shape
+    _f32(q, "latent_attention: q")
+    if out.dtype != cache.dtype or out.stride(1) != 1 or q.shape[2] != D:
+        raise KernelError("latent_attention: out in the cache's dtype, q [T, heads, D]")
+    if tracing():
+        keys = sum(min(p + 1, window) if window > 0 else p + 1
+                   for e, p0 in enumerate(ctx.host_entry_pos0)
+                   for p in range(p0, p0 + ctx.host_entry_start[e + 1] - ctx.host_entry_start[e]))
+        _note("attn", "attn", (ctx.n_rows, keys, n_head * D), keys * n_head * 2.0 * (D + kv_rank),
+              4.0 * ctx.n_rows * n_head * D + out.element_size() * (ctx.n_rows * n_head * kv_rank + keys * D))
+    _check(library().nib_latent_attention(_dt(cache), _ptr(q), _ptr(cache), _ptr(out), out.stride(0), _ptr(block_table),
+                                          block_table.shape[1], None, _ptr(ctx.row_entry), _ptr(ctx.positions),
+                                          ctx.n_rows, n_head, kv_rank, D, page_size, n_pages, float(scale),
+                                          int(window), _ptr(ctx.status), _stream()), "latent_attention")
+
+
+def linear_heads(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int,
+                 M: int) -> None:
+    """out[t, h * out_head_stride + n] = sum_k a[t, h * a_head_stride + k] * w[h, n, k] for w [heads, N, K]."""
+    H, N, K = w.shape
+    if a.dtype != w.dtype or not w.is_contiguous() or a.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("linear_heads: a and w share a dtype, w contiguous [heads, N, K]")
+    if tracing():
+        _note("matmul", "matmul_heads", (M, K, H * N), 2.0 * M * H * N * K,
+              w.numel() * w.element_size() + M * H * (K * a.element_size() + N * out.element_size()))
+    _check(library().nib_linear_heads(_dt(a), _dt(out), _ptr(a), a.stride(0), a_head_stride, _ptr(w), _ptr(out),
+                                      out.stride(0), out_head_stride, M, H, N, K, _stream()), "linear_heads")
+
+
+# ------------------------------------------------------------------------------ delta rule
+def delta_rule(proj: torch.Tensor, offsets, wl: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor,
+               norm_w: torch.Tensor, state: torch.Tensor, ctx, n_head: int, dim: int, eps: float,
+               out: torch.Tensor) -> None:
+    """The generalised delta rule over the step's entries (csrc/delta_rule.cu).  ``proj`` float32 [T, *] holds
+    r, k, v, gate and removal logits at the column ``offsets`` (five), ``wl`` float32 the decay logits; ``state``
+    float32 [slots, n_head, dim, dim] is read and written at the entries' slots."""
+    _f32(proj, "delta_rule: proj"); _f32(state, "delta_rule: state")
+    if wl.dtype != torch.float32 or wl.stride(1) != 1 or out.stride(1) != 1 or tuple(state.shape[1:]) != (n_head, dim, dim):
+        raise KernelError("delta_rule: wl float32, state [slots, heads, dim, dim]")
+    r_off, k_off, v_off, g_off, a_off = (int(o) for o in offsets)
+    if tracing():
+        T = ctx.n_rows
+        _note("other", "delta_rule", (T, n_head * dim, dim), 8.0 * T * n_head * dim * dim,
+              T * n_head * dim * (6 * 4 + out.element_size()) + 8.0 * ctx.n_entries * n_head * dim * dim)
+    _check(library().nib_delta_rule(_dt(out), _ptr(proj), proj.stride(0), r_off, k_off, v_off, g_off, a_off, _ptr(wl),
+                                    wl.stride(0), _ptr(w0), _ptr(a_bias), _ptr(norm_w), _ptr(state),
+                                    _ptr(ctx.entry_start), _ptr(ctx.entry_slot), ctx.n_entries, n_head, dim,
+                                    float(eps), _ptr(out), out.stride(0), _stream()), "delta_rule")
+
+
+# ------------------------------------------------------------------------------ routed experts
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, T: int, top: int, renorm: bool, ids: torch.Tensor,
+              weights: torch.Tensor) -> None:
+    """Router logits in 32-bit, softmax over all experts, the ``top`` largest (ties to the lower index) into
+    ``ids`` int32 [T, top] with their scores in ``weights`` float32 [T, top] (divided by their sum with ``renorm``)."""
+    E, C = w_router.shape
+    if h.dtype != w_router.dtype or h.stride(1) != 1 or not w_router.is_contiguous():
+        raise KernelError("moe_route: h and the router share a dtype")
+    _i32(ids, "ids"); _f32(weights, "moe_route: weights")
+    if tracing():
+        _note("matmul", "router", (T, C, E), 2.0 * T * C * E, (E + T) * C * h.element_size() + 8.0 * T * top)
+    _check(library().nib_moe_route(_dt(h), _ptr(h), h.stride(0), _ptr(w_router), T, C, E, top, int(renorm), _ptr(ids),
+                                   _ptr(weights), _stream()), "moe_route")
+
+
+def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, inner: torch.Tensor, T: int, top: int,
+           act: int) -> None:
+    """inner[t * top + k] = act(w_up[ids[t, k]] . h[t]) for w_up [experts, F, C]."""
+    E, F, C = w_up.shape
+    if h.dtype != w_up.dtype or inner.dtype != h.dtype or not w_up.is_contiguous() or not inner.is_contiguous() \
+            or inner.shape[1] != F:
+        raise KernelError("moe_up: h, w_up and inner share a dtype; inner contiguous [T * top, F]")
+    if tracing():
+        _note("matmul", "experts_up", (T * top, C, F), 2.0 * T * top * C * F,
+              h.element_size() * (min(E, T * top) * F * C + T * C + T * top * F))
+    _check(library().nib_moe_up(_dt(h), _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), _ptr(inner), T, C, F, top,
+                                int(act), _stream()), "moe_up")
+
+
+def moe_down(inner: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor,
+             T: int, top: int) -> None:
+    """x[t] += sum_k weights[t, k] * w_down[ids[t, k]] . inner[t * top + k] for w_down [experts, C, F]."""
+    E, C, F = w_down.shape
+    _f32(x, "moe_down: x")
+    if inner.dtype != w_down.dtype or not w_down.is_contiguous() or not inner.is_contiguous() or x.shape[1] != C:
+        raise KernelError("moe_down: inner and w_down share a dtype; x [T, C]")
+    if tracing():
+        _note("matmul", "experts_down", (T * top, F, C), 2.0 * T * top * C * F,
+              inner.element_size() * (min(E, T * top) * F * C + T * top * F) + 8.0 * T * C)
+    _check(library().nib_moe_down(_dt(inner), _ptr(inner), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(x), T, C, F,
+                                  top, _stream()), "moe_down")

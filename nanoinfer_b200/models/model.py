@@ -8,6 +8,7 @@ attends over it), then the final norm and the head on the rows whose logits are 
 """
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -55,7 +56,7 @@ class Model:
                     args["position"] = self._build(P.POSITIONS, ls.mixer_position, f"{w}.mixer_position")
                     ps = PartSpec(ps.kind, args, ps.tensors)
                 built[name] = self._build(registry, ps, f"{w}.{name}")
-            self.layers.append(cls(spec.width, built))
+            self.layers.append(cls(spec.width, built, **getattr(ls, "args", {})))
         self.final_norm = self._build(P.NORMS, spec.final_norm, "final_norm")
         self.head = self._build(P.HEADS, spec.head, "head")
         self.schedule = list(spec.schedule)
@@ -83,9 +84,10 @@ class Model:
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < i or self.schedule[e.cache_of].cache_of is not None:
                     raise ValueError(f"schedule[{i}].cache_of must name an earlier entry that owns a cache")
+                # (a reader may look back over a window of its own: the owner's pages are kept for the widest)
                 a = self._kv_spec(e.layer)
                 b = self._kv_spec(self.schedule[e.cache_of].layer)
-                if a is None or a != b:
+                if a is None or b is None or dataclasses.replace(a, window=0) != dataclasses.replace(b, window=0):
                     raise ValueError(f"schedule[{i}] cannot read the cache of entry {e.cache_of}: "
                                      f"their key/value needs differ ({a} vs {b})")
 
@@ -123,12 +125,16 @@ class Model:
 
     # ------------------------------------------------------------------ what the cache manager must provide
     def kv_needs(self) -> List[Tuple[int, P.KVCacheSpec]]:
-        """(schedule index, need) for every run that owns paged keys and values."""
+        """(schedule index, need) for every run that owns paged keys and values.  Where other runs read
+        an owner's cache through windows of their own, the owner's pages are kept for the widest of them
+        (0, all keys, being the widest)."""
         out = []
         for i, e in enumerate(self.schedule):
             spec = self._kv_spec(e.layer)
             if spec is not None and e.cache_of is None:
-                out.append((i, spec))
+                windows = [spec.window] + [self._kv_spec(r.layer).window for r in self.schedule if r.cache_of == i]
+                widest = 0 if min(windows) <= 0 else max(windows)
+                out.append((i, dataclasses.replace(spec, window=widest)))
         return out
 
     def state_needs(self) -> List[Tuple[int, P.StateSpec]]:
@@ -187,8 +193,9 @@ class Model:
         for i, e in enumerate(self.schedule):
             owner = i if e.cache_of is None else e.cache_of
             ctx.layer = i
+            ctx.next_block = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
             self.layers[e.layer].forward(x, ctx, caches.get(owner), states.get(i), e.cache_of is None, self.dtype)
-        ctx.layer = -1
+        ctx.layer, ctx.next_block = -1, None
         if n_logits <= 0:
             return None
         # the final norm runs on the wanted rows only; the head folds it into its product where it can

@@ -28,8 +28,11 @@ class LayerSpec:
     ``feed_forward``), given as keywords or as the ``parts`` dictionary."""
 
     def __init__(self, arrangement: str, parts: Optional[Dict[str, PartSpec]] = None,
-                 mixer_position: Optional[PartSpec] = None, **named: PartSpec):
+                 mixer_position: Optional[PartSpec] = None, args: Optional[Dict[str, Any]] = None,
+                 **named: PartSpec):
         self.arrangement = arrangement              # registered name of the block arrangement
+        #: constants of the arrangement itself (constructor arguments beside width and parts)
+        self.args: Dict[str, Any] = dict(args or {})
         self.parts: Dict[str, PartSpec] = {**(parts or {}), **named}
         #: a position encoding that acts inside the mixer (on queries and keys), if any
         self.mixer_position = mixer_position

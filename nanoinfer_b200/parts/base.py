@@ -53,6 +53,8 @@ class KVCacheSpec:
     n_kv_head: int
     head_dim: int
     window: int = 0          # 0: all keys; w > 0: the last w positions only
+    #: tensors per position and head: 2 (a key and a value), or 1 where one row serves as both (a latent)
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -196,6 +198,14 @@ class Mixer(Part):
         raise NotImplementedError
 
 
+class DepthMix(Part):
+    """What goes on to the next layer as a function of ALL layers' results so far (level 0 is the embedding's
+    output, level i + 1 the result of the i-th run of the schedule).  The block arrangement that holds one
+    keeps the levels and applies it; the part owns the parameters and says how many levels it reads."""
+
+    n_levels = 0
+
+
 class FeedForward(Part):
     """Per-row transformation; ``forward`` ADDS its output to the residual stream ``x``.
     ``takes_norm_input`` as for mixers."""
@@ -249,6 +259,7 @@ MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
+DEPTH_MIXES = Registry("depth mix")
 
 register_norm = NORMS.register
 register_position = POSITIONS.register
@@ -256,13 +267,14 @@ register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
+register_depth_mix = DEPTH_MIXES.register
 
 
 # ----------------------------------------------------------------------------- what a step shows to the parts
 @dataclass
 class KVCacheView:
     """One cache layer as a mixer sees it during a step."""
-    layer: torch.Tensor          # [n_pages, 2, n_kv_head, page_size, head_dim]
+    layer: torch.Tensor          # [n_pages, planes, n_kv_head, page_size, head_dim]
     block_table: torch.Tensor    # int32 [n_entries, max_blocks]; -1 where no page is held
     page_size: int
     window: int
@@ -297,6 +309,10 @@ class StepContext:
     layer: int = -1
     #: the step's plans by name (``Part.step_planner``); a part that finds none builds its own
     plans: Dict[str, StepPlan] = field(default_factory=dict)
+    #: the arrangement of the schedule entry that runs next (None behind the last): an arrangement may do the
+    #: next one's first step in its own last kernel and say so in ``stream_entered``
+    next_block: Optional[object] = None
+    stream_entered: bool = False
     #: int32 [slots]: the token last sampled for each slot, left on the device by the sampler; a
     #: negative entry -(s + 1) of ``tokens`` stands for ``token_feedback[s]``
     token_feedback: Optional[torch.Tensor] = None

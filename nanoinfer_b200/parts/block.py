@@ -10,7 +10,9 @@ from typing import Callable, ClassVar, Dict, Optional, Type
 
 import torch
 
-from .base import FEED_FORWARDS, MIXERS, NORMS, KVCacheView, Mixer, Part, Registry, StepContext, StepLimits, Workspace
+from ..kernels import ops
+from .base import (DEPTH_MIXES, FEED_FORWARDS, MIXERS, NORMS, KVCacheView, Mixer, Part, Registry, StepContext,
+                   StepLimits, Workspace)
 
 BLOCKS: Dict[str, Type["Block"]] = {}
 
@@ -26,9 +28,11 @@ class Block:
     #: part name -> the registry it is built from.  At most one of them may be a mixer: the cache
     #: manager gives a run of the layer one set of pages or one state slot tensor.
     slots: ClassVar[Dict[str, Registry]] = {}
+    #: names of ``slots`` that a layer may leave out
+    optional: ClassVar[tuple] = ()
 
     def __init__(self, width: int, parts: Dict[str, Part]):
-        missing, unknown = set(self.slots) - set(parts), set(parts) - set(self.slots)
+        missing, unknown = set(self.slots) - set(parts) - set(self.optional), set(parts) - set(self.slots)
         if missing or unknown:
             raise ValueError(f"{type(self).__name__} is made of {sorted(self.slots)}: missing {sorted(missing)}, "
                              f"unknown {sorted(unknown)}")
@@ -74,3 +78,63 @@ class PreNormBlock(Block):
     def forward(self, x, ctx, cache, state, writes_cache, dtype) -> None:
         self.mixer.forward(self._normed(self.norm_1, self.mixer, x, ctx, dtype), x, ctx, cache, state, writes_cache)
         self.feed_forward.forward(self._normed(self.norm_2, self.feed_forward, x, ctx, dtype), x, ctx)
+
+
+@register_block("post_norm_depth_mix")
+class PostNormDepthMixBlock(Block):
+    """Norm AFTER the sum, the sublayers reading the stream itself:
+        x <- norm_1(alpha * x + mixer(x));   x <- norm_2(alpha * x + feed_forward(x))
+    (a layer without a feed-forward has the first line only), and then, with a ``depth_mix``, what goes on
+    is a weighted sum of the embedding's output and ALL layers' results so far, this one's among them.
+
+    On the device the stream is kept pre-scaled: one kernel leaves the sublayer's input (the stream in the
+    engine's dtype) and alpha times the stream, into which the sublayer's last product adds; the norm that
+    follows does the same for the next sublayer in its own kernel, and the layer's last kernel (norm, the
+    level's store, the sum over levels) does it for the next layer where that is one of this arrangement."""
+
+    slots = {"norm_1": NORMS, "mixer": MIXERS, "norm_2": NORMS, "feed_forward": FEED_FORWARDS,
+             "depth_mix": DEPTH_MIXES}
+    optional = ("norm_2", "feed_forward", "depth_mix")
+
+    def __init__(self, width: int, parts: Dict[str, Part], alpha: float = 1.0):
+        super().__init__(width, parts)
+        if ("norm_2" in parts) != ("feed_forward" in parts):
+            raise ValueError("post_norm_depth_mix: norm_2 and feed_forward come together or not at all")
+        for name in ("norm_1", "norm_2"):
+            if name in parts and not hasattr(parts[name], "eps"):
+                raise ValueError(f"post_norm_depth_mix: {name} must be an RMS norm")
+        self.alpha = float(alpha)
+        self.norm_2 = parts.get("norm_2")
+        self.feed_forward = parts.get("feed_forward")
+        self.depth_mix = parts.get("depth_mix")
+
+    def reserve(self, workspace, limits) -> None:
+        workspace.reserve("block.stream_in", limits.max_rows * self.width, limits.dtype)
+        if self.depth_mix is not None:
+            workspace.reserve("block.levels", self.depth_mix.n_levels * limits.max_rows * self.width, torch.float32)
+
+    def forward(self, x, ctx, cache, state, writes_cache, dtype) -> None:
+        T, ws = ctx.n_rows, ctx.workspace
+        xn = ws.get("block.stream_in", (ctx.max_rows, self.width), dtype)
+        levels = None
+        if self.depth_mix is not None:
+            levels = ws.get("block.levels", (self.depth_mix.n_levels, ctx.max_rows, self.width), torch.float32)
+        if ctx.stream_entered:
+            ctx.stream_entered = False      # the arrangement before this one left xn and alpha * x behind
+        else:
+            first = levels is not None and self.depth_mix.n_levels == 2   # level 0 is what this layer was given
+            ops.stream_enter(x, xn, self.alpha, T, levels[0] if first else None)
+        self.mixer.forward(xn, x, ctx, cache, state, writes_cache)
+        last = self.norm_1
+        if self.feed_forward is not None:
+            ops.post_norm(x, self.norm_1.params["weight"], self.norm_1.eps, T, xn=xn, alpha_next=self.alpha)
+            self.feed_forward.forward(xn, x, ctx)
+            last = self.norm_2
+        nxt = ctx.next_block
+        fuse = isinstance(nxt, PostNormDepthMixBlock) and nxt.width == self.width
+        if fuse:
+            ctx.stream_entered = True
+        ops.post_norm(x, last.params["weight"], last.eps, T, xn=xn if fuse else None,
+                      alpha_next=nxt.alpha if fuse else 1.0, levels=levels,
+                      n_levels=self.depth_mix.n_levels if levels is not None else 0,
+                      mix=self.depth_mix.params["weights"] if levels is not None else None)

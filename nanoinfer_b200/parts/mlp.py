@@ -2,7 +2,8 @@
 (reference: crates/core/src/stages/blocks.rs:113-137).  The reference fixes the inner width
 at 4C (crates/core/src/weights.rs:95-98) and the activation at tanh-GELU
 (crates/core/src/kernels/reference.rs:53-61); both are parameters here, and the exact
-erf-GELU is offered beside the tanh form."""
+erf-GELU is offered beside the tanh form, and xIELU, an activation with two learned numbers p, q:
+z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2."""
 from __future__ import annotations
 
 from typing import List
@@ -18,8 +19,8 @@ class DenseMLP(FeedForward):
     takes_norm_input = True
 
     def __init__(self, width: int, inner: int, activation: str, bias: bool = True):
-        if activation not in ("tanh", "erf"):
-            raise ValueError(f"activation {activation!r} is not one of 'tanh', 'erf' (the two GELU forms)")
+        if activation not in ("tanh", "erf", "xielu"):
+            raise ValueError(f"activation {activation!r} is not one of 'tanh', 'erf' (the two GELU forms), 'xielu'")
         self.width, self.inner, self.activation, self.bias = int(width), int(inner), activation, bool(bias)
 
     def param_specs(self) -> List[ParamSpec]:
@@ -27,6 +28,8 @@ class DenseMLP(FeedForward):
                  ParamSpec("proj_weight", (self.width, self.inner), MATRIX)]
         if self.bias:
             specs += [ParamSpec("fc_bias", (self.inner,), VECTOR), ParamSpec("proj_bias", (self.width,), VECTOR)]
+        if self.activation == "xielu":
+            specs.append(ParamSpec("act_params", (2,), VECTOR))
         return specs
 
     def reserve(self, workspace, limits) -> None:
@@ -37,6 +40,10 @@ class DenseMLP(FeedForward):
         fc = ctx.workspace.get("mlp.fc", (ctx.max_rows, self.inner), self.dtype)
         xn, norm = (None, xn) if isinstance(xn, ops.NormInput) else (xn, None)
         ops.trace_scope(ctx.layer, "fc")
-        ops.linear(xn, p["fc_weight"], p.get("fc_bias"), fc, T, act=ops.ACT_CODES[self.activation], norm=norm)
+        if self.activation == "xielu":
+            ops.linear(xn, p["fc_weight"], p.get("fc_bias"), fc, T, norm=norm)
+            ops.unary(fc, fc, T, ops.UNARY_XIELU, p["act_params"])
+        else:
+            ops.linear(xn, p["fc_weight"], p.get("fc_bias"), fc, T, act=ops.ACT_CODES[self.activation], norm=norm)
         ops.trace_scope(ctx.layer, "fc_proj")
         ops.linear(fc, p["proj_weight"], p.get("proj_bias"), x, T, residual=True)

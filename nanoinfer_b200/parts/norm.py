@@ -35,3 +35,18 @@ class LayerNorm(Norm):
     def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int,
                 rows: Optional[torch.Tensor] = None) -> None:
         ops.layernorm(x, self.params["weight"], self.params["bias"], self.eps, out, n_rows, rows)
+
+
+@register_norm("rmsnorm")
+class RMSNorm(Norm):
+    """x / sqrt(mean(x^2) + eps) * weight, the eps inside the root; statistics in 32-bit."""
+
+    def __init__(self, width: int, eps: float):
+        self.width, self.eps = int(width), float(eps)
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [ParamSpec("weight", (self.width,), VECTOR, INIT_ONE_PLUS_NORMAL)]
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int,
+                rows: Optional[torch.Tensor] = None) -> None:
+        ops.rmsnorm(x, self.params["weight"], self.eps, out, n_rows, rows)

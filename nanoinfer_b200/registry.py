@@ -45,10 +45,24 @@ def architectures():
 
 
 def load_config(model_dir: str) -> ModelConfig:
-    """Read ``model_dir/config.json`` into the typed configuration of its architecture."""
+    """Read ``model_dir/config.json`` into the typed configuration of its architecture.  A configuration
+    that leaves sizes to the checkpoint's tensor shapes (``sizes_from_tensors``) is shown the header of
+    ``model_dir/model.safetensors`` where that file exists."""
+    import os
+
     raw = read_config_json(model_dir)
     arch = get_architecture(architecture_name(raw))
-    return arch.config_cls.from_dict(raw)
+    cfg = arch.config_cls.from_dict(raw)
+    path = os.path.join(model_dir, "model.safetensors")
+    if hasattr(cfg, "sizes_from_tensors") and os.path.isfile(path):
+        from .weights.safetensors_io import SafetensorsFile
+
+        st = SafetensorsFile(path)
+        try:
+            cfg.sizes_from_tensors({name: tuple(st.info(name).shape) for name in st.names()})
+        finally:
+            st.close()
+    return cfg
 
 
 def _register_builtin() -> None:
@@ -56,6 +70,11 @@ def _register_builtin() -> None:
     from .models.gpt2 import build_gpt2_spec
 
     register_architecture("GPT2LMHeadModel", GPT2Config, build_gpt2_spec)
+
+    from .config.vadonex import VadonexConfig
+    from .models.vadonex import build_vadonex_spec
+
+    register_architecture("Vadonex", VadonexConfig, build_vadonex_spec)
 
 
 _register_builtin()
