@@ -207,10 +207,26 @@ class CacheManager:
         self._live: List[RequestCache] = []
         # the longest block table a request can have, per group
         self.max_blocks = [self._max_blocks(g) for g in self.groups]
+        #: goes up whenever a group's block tables had to be made longer (``_grow_tables``): whoever sized
+        #: buffers by ``max_blocks`` compares it before a step
+        self.table_generation = 0
 
     def _max_blocks(self, g: CacheGroup) -> int:
         limit = self.max_positions if self.max_positions is not None else g.pool.n_pages * self.page_size
         return max(1, -(-limit // self.page_size))
+
+    def _grow_tables(self, gi: int, n_blocks: int) -> None:
+        """A model without a position limit, a group that keeps a window of keys: a request may become longer
+        than the whole pool holds (pages behind the window go back), so its block table, one entry per
+        logical block from position 0 on, outgrows what the pool's size gave it.  The tables of the group
+        are then made at least twice as long."""
+        new = max(2 * self.max_blocks[gi], n_blocks)
+        self.max_blocks[gi] = new
+        for r in self._live:
+            row = np.full(new, -1, dtype=np.int32)
+            row[:len(r.table_rows[gi])] = r.table_rows[gi]
+            r.table_rows[gi] = row
+        self.table_generation += 1
 
     # ------------------------------------------------------------------ requests
     def open_request(self) -> RequestCache:
@@ -275,6 +291,9 @@ class CacheManager:
             raise PoolExhausted("KV cache pool exhausted: the step needs more pages than are free")
         for req, n in work:
             n_blocks = -(-(req.n_tokens + n) // self.page_size)
+            for gi, g in enumerate(self.groups):
+                if n_blocks > self.max_blocks[gi]:
+                    self._grow_tables(gi, n_blocks)
             for g, blocks, row in zip(self.groups, req.blocks, req.table_rows):
                 while len(blocks) < n_blocks:
                     page = g.pool.take()

@@ -121,18 +121,7 @@ class ModelRunner:
         model.reserve(self.workspace, StepLimits(self.max_rows, self.max_entries, int(limit), model.dtype))
         self._graph_generation = self.workspace.generation
         self.status = ops.status_word() if on_gpu else torch.zeros(1, dtype=torch.int32)
-        n_tables = sum(self.max_entries * mb for mb in cache.max_blocks)
-        cap = 7 * self.max_rows + 8 * self.max_entries + 16 + n_tables
-        # A ring of pinned staging buffers: a buffer is written again only after the copy that
-        # last read it has finished.
-        self._ring = []
-        for _ in range(4):
-            host = torch.empty(cap, dtype=torch.int32)
-            if on_gpu:
-                host = host.pin_memory()
-            self._ring.append((host, host.numpy(), torch.cuda.Event() if on_gpu else None))
-        self._ring_next = 0
-        self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self._size_tables()
         self._arange = np.arange(self.max_entries + 1, dtype=np.int32)
         self._graphs: Dict[tuple, _Captured] = {}
         #: how often the graphs had to be dropped because a scratch buffer was replaced
@@ -147,6 +136,23 @@ class ModelRunner:
         self.last_logit_slot = None
         #: kernel launches of the last step (counted by the kernel interface)
         self.launches_last_step = 0
+
+    def _size_tables(self) -> None:
+        """The step's packed tables on the host (a ring of pinned staging buffers: a buffer is written again
+        only after the copy that last read it has finished) and on the device, sized by the longest block
+        tables the cache manager hands out."""
+        on_gpu = self.device.type == "cuda"
+        n_tables = sum(self.max_entries * mb for mb in self.cache.max_blocks)
+        cap = 7 * self.max_rows + 8 * self.max_entries + 16 + n_tables
+        self._ring = []
+        for _ in range(4):
+            host = torch.empty(cap, dtype=torch.int32)
+            if on_gpu:
+                host = host.pin_memory()
+            self._ring.append((host, host.numpy(), torch.cuda.Event() if on_gpu else None))
+        self._ring_next = 0
+        self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self._table_generation = getattr(self.cache, "table_generation", 0)
 
     # ------------------------------------------------------------------ checks
     def _validate(self, items: Sequence[StepItem], feedback: bool = False) -> int:
@@ -261,6 +267,12 @@ class ModelRunner:
         and is valid until the next step."""
         T = self._validate(items, feedback=sampler is not None and hasattr(sampler, "last_token"))
         self.cache.append([(it.request, len(it.tokens)) for it in items])  # all pages of the step, or none
+        if getattr(self.cache, "table_generation", 0) != self._table_generation:
+            # the block tables grew (a request behind a window, longer than the pool): every graph bakes in
+            # their length and the address of the packed tables, so the graphs go before the buffers do
+            if self.device.type == "cuda":
+                self._drop_graphs()
+            self._size_tables()
         E = len(items)
         decode_only = T == E
         host, buf, copied = self._ring[self._ring_next]
