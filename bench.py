@@ -3,6 +3,11 @@
 weights, bfloat16) at batch 8 on one B200, with prefill, roofline and end-to-end figures.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--preset NAME]
+    python bench.py --compare-designs [--widths 768,1024,1600] [--layers 4]
+
+With --compare-designs another line is printed instead: Vadonex (latent attention, delta rule, routed
+experts) beside GPT-2 at equal width, depth, vocabulary and context, prefill and decode throughput and each
+op's fraction of its roofline (``bench_support.compare_designs``).  The default workload is as before.
 
 One JSON line is printed.  A "step" is one decode step of the whole batch.
   value      decoded tokens per second, device-timed (CUDA events) around each step's kernels,
@@ -55,6 +60,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the preset (recorded in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out the points at batch 1 and 64")
     ap.add_argument("--skip-workloads", action="store_true", help="leave out the workloads object")
+    ap.add_argument("--compare-designs", action="store_true",
+                    help="Vadonex beside GPT-2 at equal layer sizes instead of the headline workload")
+    ap.add_argument("--widths", default="768,1024,1600", help="with --compare-designs: the model widths")
     ap.add_argument("--preheat", type=float, default=1.5,
                     help="seconds of untimed prefill steps before the timed loops (0: none)")
     args = ap.parse_args()
@@ -71,6 +79,13 @@ def main() -> int:
     import torch
 
     from nanoinfer_b200 import bench_support as bs
+
+    if args.compare_designs:
+        sizes = bs.compare_designs([int(w) for w in args.widths.split(",")], n_layer=args.layers or 4,
+                                   batch=args.batch, steps=min(args.steps, 64), warmup=max(3, args.warmup))
+        print(json.dumps({"metric": "designs side by side", "dtype": "bf16", "data": "synthetic",
+                          "peaks": bs.measured_peaks(), "sizes": sizes, "provenance": bs.provenance()}))
+        return 0
 
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)

@@ -395,6 +395,127 @@ def print_profile(eng, prompt, out=None) -> None:
     eng.cache.close_request(r)
 
 
+# ----------------------------------------------------------------------------- two designs side by side
+def vadonex_like(width: int, n_layer: int, vocab: int, window: int) -> dict:
+    """A Vadonex configuration whose layers have the sizes of a GPT-2 of ``width`` (heads of 64, inner width
+    4 x width): by turns a delta-rule layer with a dense feed-forward, a latent-attention layer with routed
+    experts, a latent-attention layer that reads the one before, and a delta-rule layer with routed experts."""
+    heads = width // 64
+    att = dict(heads=heads, dim=64, rot_dim=32, vdim=64, q_rank=width // 2, kv_rank=256, scale=96 ** -0.5,
+               mask=dict(size=window), rot=dict(base=10000.0, dims=32))
+    moe = dict(kind="moe", router=dict(experts=8, top=2), expert=dict(ff=width), shared=dict(ff=width))
+    delta = dict(heads=heads, dim=64, decay_rank=64)
+    layers = []
+    for i in range(n_layer):
+        kind = i % 4
+        if kind == 0:
+            layers.append(dict(type="general_delta", mixer=dict(delta), mlp=dict(kind="dense", ff=4 * width)))
+        elif kind == 1:
+            layers.append(dict(type="latent_attention", mixer=dict(att), mlp=dict(moe)))
+        elif kind == 2:
+            layers.append(dict(type="latent_attention", mixer=dict(att, kv_from=i - 1), mlp=dict(moe)))
+        else:
+            layers.append(dict(type="general_delta", mixer=dict(delta), mlp=dict(moe)))
+    return dict(architecture="Vadonex", vocab=vocab, width=width, postln_alpha=2.0, norm=dict(eps=1e-6), layers=layers)
+
+
+def folder_of(raw: dict, seed: int, dtype: torch.dtype) -> str:
+    """A folder with seeded random weights of the configuration ``raw`` (made once, in the temporary folder)."""
+    from .config.base import architecture_name
+    from .registry import get_architecture
+    from .weights.random_init import write_random_model
+
+    cfg = get_architecture(architecture_name(raw)).config_cls.from_dict(json.loads(json.dumps(raw)))
+    key = hashlib.sha1(json.dumps([raw, seed, str(dtype)], sort_keys=True).encode()).hexdigest()[:12]
+    d = os.path.join(tempfile.gettempdir(), f"nanoinfer_b200_model_{os.getuid()}_{key}")
+    if not os.path.isfile(os.path.join(d, "model.safetensors")):
+        write_random_model(cfg, d, seed, dtype)
+    return d
+
+
+def profile_forward(eng, prompt, batch: int, repeats: int = 3):
+    """(prefill table, decode table), name -> (calls, ms, FLOPs, bytes) per step, of one prompt run in one step
+    and of decode steps of ``batch`` requests behind that prompt, kernels launched one by one under a trace
+    recorder.  Nothing is cut back (a mixer with state cannot be): every repeat runs on requests of its own, and
+    the decode steps follow one another."""
+    from . import trace
+    from .engine.runner import StepItem
+
+    graphs = eng.runner.use_graphs
+    eng.runner.use_graphs = False
+    n = len(prompt)
+    try:
+        def fresh():
+            r = eng.cache.open_request()
+            eng.runner.step([StepItem(r, prompt, [n - 1])])
+            return r
+        eng.cache.close_request(fresh())
+        rec = trace.start()
+        for _ in range(repeats):
+            rec.begin_step("prefill", n, 0)
+            eng.cache.close_request(fresh())
+        pre = rec.table()
+        trace.stop()
+        reqs = [fresh() for _ in range(batch)]
+        eng.runner.step([StepItem(r, [1], [0]) for r in reqs])
+        rec = trace.start()
+        for _ in range(repeats):
+            rec.begin_step("decode", batch, n)
+            eng.runner.step([StepItem(r, [1], [0]) for r in reqs])
+        dec = rec.table()
+        for r in reqs:
+            eng.cache.close_request(r)
+    finally:
+        trace.stop()
+        eng.runner.use_graphs = graphs
+    per = lambda table: {k: (c // repeats, ms / repeats, fl / repeats, by / repeats) for k, (c, ms, fl, by) in table.items()}
+    return per(pre), per(dec)
+
+
+def compare_designs(widths=(768, 1024, 1600), n_layer: int = 4, batch: int = 8, context: int = 1024,
+                    steps: int = 64, warmup: int = 8) -> List[dict]:
+    """Vadonex beside GPT-2 at equal width, depth, vocabulary and context (random weights, bfloat16): one
+    prompt of ``context - steps - warmup`` tokens in one step, decode at ``batch``, and where the time of
+    each goes op by op with every op's fraction of its roofline (measured peaks)."""
+    peaks = measured_peaks()
+    out = []
+    for width in widths:
+        gpt2 = dict(architectures=["GPT2LMHeadModel"], vocab_size=50257, n_positions=context, n_embd=width,
+                    n_layer=n_layer, n_head=width // 64, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+        record = {"width": width, "n_layer": n_layer, "batch": batch, "context": context}
+        for name, raw in (("vadonex", vadonex_like(width, n_layer, 50257, context)), ("gpt2", gpt2)):
+            d = folder_of(raw, 1234, torch.bfloat16)
+            eng = build_engine(d, "bfloat16", batch, context, max_rows=2048)
+            preheat(eng, 0.5)
+            prompt_len = context - steps - warmup
+            pre = time_prefill(eng, 1, prompt_len, runs=3, warmup=4)
+            dec = time_decode(eng, batch, prompt_len, steps, warmup)
+            prompt = [(7 * i + 1) % eng.model.vocab_size for i in range(prompt_len)]
+            ops_pre, ops_dec = profile_forward(eng, prompt, batch)
+
+            def rows(table):
+                res = {}
+                for op, (n, ms, fl, by) in table.items():
+                    ideal = max(fl / (peaks["bf16_tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9))
+                    res[op] = {"calls": n, "ms": round(ms, 4), "of_roofline": round(ideal / (ms / 1e3 or 1e-12), 4)}
+                return res
+
+            record[name] = {
+                "params_m": round(parameter_count(eng.model) / 1e6, 1),
+                "prefill_tok_s": round(pre["tokens_per_s"]), "prefill_ms": round(pre["ms"], 3),
+                "prefill_frac_of_bf16_peak": round(pre["flops"] / (pre["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
+                "decode_tok_s": round(dec["tokens_per_s"]), "decode_ms_per_step": round(dec["ms_per_step"], 4),
+                "decode_frac_of_hbm": round((weight_bytes_per_step(eng.model) + kv_bytes(eng.cache, [dec["mean_context"]] * batch))
+                                            / (dec["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4),
+                "launches_per_decode_step": dec["launches_per_step"],
+                "prefill_ops": rows(ops_pre), "decode_ops": rows(ops_dec),
+            }
+            del eng
+            torch.cuda.empty_cache()
+        out.append(record)
+    return out
+
+
 # ----------------------------------------------------------------------------- the bench command
 def decode_points(model_dir: str, dtype: str, batches, prompt_len: int, tokens: int, warmup: int = 3,
                   bandwidth_gbs: Optional[float] = None, runs: int = 3, profile: bool = False) -> List[dict]:

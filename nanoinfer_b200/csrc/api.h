@@ -161,7 +161,7 @@ int nib_rope_heads(int dtype, const void* q, int ldq, int nope, int rot_dim, int
 int nib_latent_attention(int dtype, const float* q, const void* cache, void* out, int ldo, const int* block_table,
                          int max_blocks, const int* rows, const int* row_entry, const int* positions, int n_rows,
                          int n_head, int kv_rank, int D, int page_size, int n_pages, float scale, int window,
-                         int* status, cudaStream_t stream);
+                         int* status, int n_splits, float* partials, cudaStream_t stream);
 
 // ---- a product per head (linear_heads.cu): out[t, h, :N] = a[t, h, :K] . w[h]^T, w [n_head, N, K]
 int nib_linear_heads(int dtype, int out_dtype, const void* a, int lda, int a_head_stride, const void* w, void* out,
@@ -169,9 +169,9 @@ int nib_linear_heads(int dtype, int out_dtype, const void* a, int lda, int a_hea
 
 // ---- the generalised delta rule (delta_rule.cu)
 int nib_delta_rule(int dtype, const float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off,
-                   const float* wl, int ld_w, const float* w0, const float* a_bias, const float* norm_w,
-                   float* state, const int* entry_start, const int* entry_slot, int n_entries, int n_head, int dim,
-                   float eps, void* out, int ldo, cudaStream_t stream);
+                   float* wl, int ld_w, const float* w0, const float* a_bias, const float* norm_w,
+                   float* state, const int* entry_start, const int* entry_slot, int n_entries, int n_rows, int n_head,
+                   int dim, float eps, void* out, int ldo, cudaStream_t stream);
 
 // ---- a routed feed-forward (moe.cu)
 int nib_moe_route(int dtype, const void* h, int ldh, const void* w_router, int T, int C, int n_expert, int top,

@@ -7,9 +7,15 @@
 //   S_t = diag(w) S_(t-1) - (a * u) (u^T S_(t-1)) + k v^T        (both terms read the old state)
 //   o_t = S_t^T r
 // then each head's o is divided by its root mean square, multiplied by a weight and by sigmoid(gate).
-// One block per (batch entry, head) walks the entry's rows in order; thread j owns value channel j, the
-// state lives in shared memory as 32-bit floats and goes back to the request's slot at the end.  The
-// projections come in as 32-bit floats; everything here is 32-bit.
+// One block per (batch entry, head) walks the entry's rows in order; thread j owns value channel j (a column
+// of S: the columns do not see one another).  For head sizes that are multiples of 16 up to 128 the column
+// lives in the thread's registers, every token's per-channel vectors (r, k, w, a u, u) are made by the
+// channel's thread for the NEXT token while this one is worked on and passed through a double buffer in
+// shared memory (one barrier a token), the raw outputs take the place of the decay logits already used, and
+// the division by each head's root mean square is a pass over the rows afterwards (inside the kernel for a
+// step of single tokens, else a kernel of its own with a warp a row and head).  Other head sizes keep the
+// state in shared memory.  The state goes back to the request's slot at the end.  The projections come in
+// as 32-bit floats; everything here is 32-bit.
 #include "api.h"
 #include "common.cuh"
 
@@ -81,20 +87,198 @@ __global__ void delta_rule_kernel(const float* proj, int ld, int r_off, int k_of
   for (int i = threadIdx.x; i < dim * dim; i += blockDim.x) slot[i] = S[i];
 }
 
+template <int DIM> struct DeltaInputs {
+  float r, k, a, w, v, ks[(DIM + 31) / 32];
+};
+
+// o[t, head] / rms * weight * sigmoid(gate) for the rows t = first, first + step, ... below `end`; a warp a row.
+template <typename T, int DIM>
+__device__ __forceinline__ void delta_finish_rows(const float* proj, int ld, int g_off, const float* raw, int ld_w,
+                                                  const float* __restrict__ norm_w, int h, float eps, T* out, int ldo,
+                                                  int first, int end, int step, int lane) {
+  constexpr int M = (DIM + 31) / 32;
+  for (int t = first; t < end; t += step) {
+    float ov[M], ss = 0.0f;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const int i = lane + 32 * m;
+      ov[m] = i < DIM ? raw[(size_t)t * ld_w + h * DIM + i] : 0.0f;
+      ss += ov[m] * ov[m];
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)DIM + eps);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const int i = lane + 32 * m;
+      if (i < DIM) {
+        const int col = h * DIM + i;
+        out[(size_t)t * ldo + col] =
+            from_float<T>(ov[m] * rstd * norm_w[col] * sigmoid_f(proj[(size_t)t * ld + g_off + col]));
+      }
+    }
+  }
+}
+
+template <typename T, int DIM>
+__global__ void __launch_bounds__((DIM + 31) / 32 * 32)
+delta_rule_reg_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off, float* wl,
+                      int ld_w, const float* __restrict__ w0, const float* __restrict__ a_bias,
+                      const float* __restrict__ norm_w, float* state, const int* __restrict__ entry_start,
+                      const int* __restrict__ entry_slot, int n_head, float eps, T* out, int ldo, int finish_inside) {
+  pdl_trigger();
+  constexpr int NT = (DIM + 31) / 32 * 32, M = (DIM + 31) / 32;
+  __shared__ __align__(16) float st[2][5][DIM];     // r, k, w, a u, u of the token at hand and of the next
+  const int e = blockIdx.x, h = blockIdx.y, j = threadIdx.x, lane = j & 31;
+  const bool on = j < DIM;
+  const int col = h * DIM + (on ? j : 0);
+  const int t0 = entry_start[e], t1 = entry_start[e + 1];
+  float* slot = state + ((size_t)entry_slot[e] * n_head + h) * (size_t)DIM * DIM;
+  const float w0j = w0[col], abj = a_bias[col];
+  pdl_wait();
+  if (t0 >= t1) return;
+  float S[DIM];
+#pragma unroll
+  for (int i = 0; i < DIM; ++i) S[i] = on ? slot[i * DIM + j] : 0.0f;
+
+  DeltaInputs<DIM> in;
+  auto load = [&](int t) {
+    const float* p = proj + (size_t)t * ld;
+    in.r = p[r_off + col]; in.k = p[k_off + col]; in.a = p[a_off + col]; in.v = p[v_off + col];
+    in.w = wl[(size_t)t * ld_w + col];
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const int i = lane + 32 * m;
+      in.ks[m] = i < DIM ? p[k_off + h * DIM + i] : 0.0f;
+    }
+  };
+  auto finish = [&](int buf) {       // every warp sums the head's k^2 on its own: no barrier
+    float ks = 0.0f;
+#pragma unroll
+    for (int m = 0; m < M; ++m) ks += in.ks[m] * in.ks[m];
+    ks = warp_sum(ks);
+    if (on) {
+      const float u = in.k / sqrtf(ks + 1e-6f);
+      st[buf][0][j] = in.r;
+      st[buf][1][j] = in.k;
+      st[buf][2][j] = expf(-0.6065306597126334f * sigmoid_f(in.w + w0j));
+      st[buf][3][j] = sigmoid_f(in.a + abj) * u;
+      st[buf][4][j] = u;
+    }
+  };
+  load(t0);
+  finish(0);
+  float vc = in.v;
+  __syncthreads();
+  int cur = 0;
+  for (int t = t0; t < t1; ++t) {
+    const bool more = t + 1 < t1;
+    if (more) load(t + 1);           // asked for now, used after this token's arithmetic
+    const float4* r4 = reinterpret_cast<const float4*>(st[cur][0]);
+    const float4* k4 = reinterpret_cast<const float4*>(st[cur][1]);
+    const float4* w4 = reinterpret_cast<const float4*>(st[cur][2]);
+    const float4* a4 = reinterpret_cast<const float4*>(st[cur][3]);
+    const float4* u4 = reinterpret_cast<const float4*>(st[cur][4]);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < DIM / 4; ++i) {
+      const float4 u = u4[i];
+      s0 += u.x * S[4 * i]; s1 += u.y * S[4 * i + 1]; s2 += u.z * S[4 * i + 2]; s3 += u.w * S[4 * i + 3];
+    }
+    const float sa = (s0 + s1) + (s2 + s3);
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < DIM / 4; ++i) {
+      const float4 w = w4[i], a = a4[i], k = k4[i], r = r4[i];
+      S[4 * i] = w.x * S[4 * i] - a.x * sa + k.x * vc;             o0 += S[4 * i] * r.x;
+      S[4 * i + 1] = w.y * S[4 * i + 1] - a.y * sa + k.y * vc;     o1 += S[4 * i + 1] * r.y;
+      S[4 * i + 2] = w.z * S[4 * i + 2] - a.z * sa + k.z * vc;     o2 += S[4 * i + 2] * r.z;
+      S[4 * i + 3] = w.w * S[4 * i + 3] - a.w * sa + k.w * vc;     o3 += S[4 * i + 3] * r.w;
+    }
+    if (on) wl[(size_t)t * ld_w + col] = (o0 + o1) + (o2 + o3);    // the raw output where the decay logit was
+    if (more) {
+      finish(cur ^ 1);
+      vc = in.v;
+    }
+    __syncthreads();
+    cur ^= 1;
+  }
+  if (on) {
+#pragma unroll
+    for (int i = 0; i < DIM; ++i) slot[i * DIM + j] = S[i];
+  }
+  if (finish_inside)
+    delta_finish_rows<T, DIM>(proj, ld, g_off, wl, ld_w, norm_w, h, eps, out, ldo, t0 + (j >> 5), t1, NT / 32, lane);
+}
+
+template <typename T, int DIM>
+__global__ void __launch_bounds__(256)
+delta_finish_kernel(const float* proj, int ld, int g_off, const float* raw, int ld_w, const float* __restrict__ norm_w,
+                    int n_head, float eps, T* out, int ldo, int n_rows) {
+  pdl_trigger();
+  const int w = blockIdx.x * 8 + (threadIdx.x >> 5);      // (row, head) pairs, a warp each
+  pdl_wait();
+  if (w >= n_rows * n_head) return;
+  const int t = w / n_head, h = w % n_head;
+  delta_finish_rows<T, DIM>(proj, ld, g_off, raw, ld_w, norm_w, h, eps, out, ldo, t, t + 1, 1, threadIdx.x & 31);
+}
+
+template <typename T, int DIM>
+static int launch_delta_reg(const float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off, float* wl,
+                            int ld_w, const float* w0, const float* a_bias, const float* norm_w, float* state,
+                            const int* entry_start, const int* entry_slot, int n_entries, int n_rows, int n_head,
+                            float eps, T* out, int ldo, cudaStream_t stream) {
+  const int inside = n_rows == n_entries;     // single tokens: the norm of a row costs less than a launch
+  launch_pdl(delta_rule_reg_kernel<T, DIM>, dim3(n_entries, n_head), dim3((DIM + 31) / 32 * 32), 0, stream, proj, ld,
+             r_off, k_off, v_off, g_off, a_off, wl, ld_w, w0, a_bias, norm_w, state, entry_start, entry_slot, n_head,
+             eps, out, ldo, inside);
+  if (!inside)
+    launch_pdl(delta_finish_kernel<T, DIM>, dim3((n_rows * n_head + 7) / 8), dim3(256), 0, stream, proj, ld, g_off,
+               (const float*)wl, ld_w, norm_w, n_head, eps, out, ldo, n_rows);
+  NIB_LAUNCH_CHECK();
+}
+
+template <typename T>
+static int pick_delta_reg(int dim, const float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off,
+                          float* wl, int ld_w, const float* w0, const float* a_bias, const float* norm_w, float* state,
+                          const int* entry_start, const int* entry_slot, int n_entries, int n_rows, int n_head,
+                          float eps, T* out, int ldo, cudaStream_t stream) {
+#define NIB_DELTA(D)                                                                                                \
+  case D:                                                                                                           \
+    return launch_delta_reg<T, D>(proj, ld, r_off, k_off, v_off, g_off, a_off, wl, ld_w, w0, a_bias, norm_w, state, \
+                                  entry_start, entry_slot, n_entries, n_rows, n_head, eps, out, ldo, stream)
+  switch (dim) {
+    NIB_DELTA(16); NIB_DELTA(32); NIB_DELTA(48); NIB_DELTA(64); NIB_DELTA(80); NIB_DELTA(96); NIB_DELTA(112);
+    NIB_DELTA(128);
+  }
+#undef NIB_DELTA
+  return NIB_ERR_UNSUPPORTED_SIZE;
+}
+
 }  // namespace nib
 
 using namespace nib;
 
 // proj: float [T, ld] holding r, k, v, gate logits and removal logits at the given column offsets (n_head *
 // dim columns each); wl: float [T, ld_w] decay logits before their bias w0.  state: float [slots, n_head,
-// dim, dim].  out: [T, n_head * dim] in `dtype`.
+// dim, dim].  out: [T, n_head * dim] in `dtype`.  n_rows: the rows of all entries together.  wl is scratch
+// afterwards (the kernel for head sizes in steps of 16 leaves its raw outputs there).
 extern "C" int nib_delta_rule(int dtype, const float* proj, int ld, int r_off, int k_off, int v_off, int g_off,
-                              int a_off, const float* wl, int ld_w, const float* w0, const float* a_bias,
+                              int a_off, float* wl, int ld_w, const float* w0, const float* a_bias,
                               const float* norm_w, float* state, const int* entry_start, const int* entry_slot,
-                              int n_entries, int n_head, int dim, float eps, void* out, int ldo,
+                              int n_entries, int n_rows, int n_head, int dim, float eps, void* out, int ldo,
                               cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if (dim <= 0 || dim > 224 || n_head <= 0) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (dim % 16 == 0 && dim <= 128) {
+    if (dtype == DT_F32)
+      return pick_delta_reg<float>(dim, proj, ld, r_off, k_off, v_off, g_off, a_off, wl, ld_w, w0, a_bias, norm_w,
+                                   state, entry_start, entry_slot, n_entries, n_rows, n_head, eps, (float*)out, ldo,
+                                   stream);
+    if (dtype == DT_BF16)
+      return pick_delta_reg<bf16>(dim, proj, ld, r_off, k_off, v_off, g_off, a_off, wl, ld_w, w0, a_bias, norm_w,
+                                  state, entry_start, entry_slot, n_entries, n_rows, n_head, eps, (bf16*)out, ldo,
+                                  stream);
+    return NIB_ERR_BAD_ARGUMENT;
+  }
   const size_t smem = ((size_t)dim * dim + 5 * (size_t)dim) * sizeof(float);
   const int threads = (dim + 31) / 32 * 32;
   const dim3 grid(n_entries, n_head);

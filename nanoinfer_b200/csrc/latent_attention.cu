@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32)
 latent_attention_kernel(const float* q, const T* cache, T* out, int ldo, const int* __restrict__ block_table,
                         int max_blocks, const int* __restrict__ rows, const int* __restrict__ row_entry,
                         const int* __restrict__ positions, int n_head, int kv_rank, int D, int page_size,
-                        int n_pages, float scale, int window, int* status) {
+                        int n_pages, float scale, int window, int* status, int n_splits, float* partials) {
   pdl_trigger();
   extern __shared__ float smem[];
   const int Dp = D | 1;
@@ -123,7 +123,14 @@ latent_attention_kernel(const float* q, const T* cache, T* out, int ldo, const i
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y * LA_WARPS + warp;
   const bool live = h < n_head;
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  int hi = pos;
+  if (n_splits > 1) {
+    // the row's own key range cut into n_splits equal pieces of whole tiles; this block takes piece blockIdx.z
+    const int per = ((pos - lo + n_splits) / n_splits + LA_TILE - 1) / LA_TILE * LA_TILE;
+    lo += blockIdx.z * per;
+    hi = min(pos, lo + per - 1);
+  }
   pdl_wait();
   if (live) {
     const float* src = q + ((size_t)t * n_head + h) * D;
@@ -132,12 +139,12 @@ latent_attention_kernel(const float* q, const T* cache, T* out, int ldo, const i
   float m = -INFINITY, l = 0.0f, acc[NACC];
 #pragma unroll
   for (int k = 0; k < NACC; ++k) acc[k] = 0.0f;
-  for (int j0 = lo; j0 <= pos; j0 += LA_TILE) {
+  for (int j0 = lo; j0 <= hi; j0 += LA_TILE) {
     __syncthreads();                            // the tile before is done with
     if (threadIdx.x < LA_TILE) {
       const int j = j0 + threadIdx.x;
       int page = -1;
-      if (j <= pos) {
+      if (j <= hi) {
         page = block_table[(size_t)entry * max_blocks + j / page_size];
         if (page < 0 || page >= n_pages) {
           *status = NIB_STATUS_BAD_PAGE;
@@ -160,14 +167,14 @@ latent_attention_kernel(const float* q, const T* cache, T* out, int ldo, const i
       const float* qh = qs + warp * D;
       float s = 0.0f;
       for (int d = 0; d < D; ++d) s += qh[d] * kr[d];
-      s = (j0 + lane <= pos && key_page[lane] >= 0) ? s * scale : -INFINITY;
+      s = (j0 + lane <= hi && key_page[lane] >= 0) ? s * scale : -INFINITY;
       const float m_new = fmaxf(m, warp_max(s));
       const float p = (s == -INFINITY) ? 0.0f : expf(s - m_new);
       const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
       l = l * corr + warp_sum(p);
 #pragma unroll
       for (int k = 0; k < NACC; ++k) acc[k] *= corr;
-      const int n_keys = min(LA_TILE, pos - j0 + 1);
+      const int n_keys = min(LA_TILE, hi - j0 + 1);
       for (int jj = 0; jj < n_keys; ++jj) {
         const float pj = __shfl_sync(0xffffffffu, p, jj);
         const float* row = ktile + jj * Dp;
@@ -180,7 +187,19 @@ latent_attention_kernel(const float* q, const T* cache, T* out, int ldo, const i
       m = m_new;
     }
   }
-  if (live) {
+  if (live && n_splits > 1) {
+    // (maximum, sum, unscaled weighted sum) of this piece: the merge kernel puts the pieces together
+    float* dst = partials + (((size_t)t * n_head + h) * n_splits + blockIdx.z) * (size_t)(kv_rank + 2);
+    if (lane == 0) {
+      dst[0] = m;
+      dst[1] = l;
+    }
+#pragma unroll
+    for (int k = 0; k < NACC; ++k) {
+      const int d = lane + 32 * k;
+      if (d < kv_rank) dst[2 + d] = acc[k];
+    }
+  } else if (live) {
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
     T* o = out + (size_t)t * ldo + (size_t)h * kv_rank;
 #pragma unroll
@@ -191,18 +210,51 @@ latent_attention_kernel(const float* q, const T* cache, T* out, int ldo, const i
   }
 }
 
+// One block per (row, head): the pieces of a row's keys, each with its own maximum, put together in the
+// order of the pieces.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* partials, T* out, int ldo, const int* __restrict__ rows,
+                    const int* __restrict__ row_entry, int n_head, int kv_rank, int n_splits) {
+  pdl_trigger();
+  const int t = rows ? rows[blockIdx.x] : blockIdx.x, h = blockIdx.y;
+  if (row_entry[t] < 0) return;
+  pdl_wait();
+  const float* src = partials + ((size_t)t * n_head + h) * n_splits * (size_t)(kv_rank + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, src[(size_t)s * (kv_rank + 2)]);
+  float l = 0.0f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = src[(size_t)s * (kv_rank + 2)];
+    if (ms != -INFINITY) l += src[(size_t)s * (kv_rank + 2) + 1] * expf(ms - m);
+  }
+  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
+    float a = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = src[(size_t)s * (kv_rank + 2)];
+      if (ms != -INFINITY) a += src[(size_t)s * (kv_rank + 2) + 2 + d] * expf(ms - m);
+    }
+    out[(size_t)t * ldo + (size_t)h * kv_rank + d] = from_float<T>(a * inv);
+  }
+}
+
 template <typename T, int NACC>
 static int launch_latent_attention(const float* q, const T* cache, T* out, int ldo, const int* block_table,
                                    int max_blocks, const int* rows, const int* row_entry, const int* positions,
                                    int n_rows, int n_head, int kv_rank, int D, int page_size, int n_pages,
-                                   float scale, int window, int* status, cudaStream_t stream) {
+                                   float scale, int window, int* status, int n_splits, float* partials,
+                                   cudaStream_t stream) {
   const size_t smem = ((size_t)LA_TILE * (D | 1) + (size_t)LA_WARPS * D) * sizeof(float);
   if (smem > 200 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(latent_attention_kernel<T, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  launch_pdl(latent_attention_kernel<T, NACC>, dim3(n_rows, (n_head + LA_WARPS - 1) / LA_WARPS), dim3(LA_WARPS * 32),
-             smem, stream, q, cache, out, ldo, block_table, max_blocks, rows, row_entry, positions, n_head, kv_rank,
-             D, page_size, n_pages, scale, window, status);
+  launch_pdl(latent_attention_kernel<T, NACC>, dim3(n_rows, (n_head + LA_WARPS - 1) / LA_WARPS, n_splits),
+             dim3(LA_WARPS * 32), smem, stream, q, cache, out, ldo, block_table, max_blocks, rows, row_entry, positions,
+             n_head, kv_rank, D, page_size, n_pages, scale, window, status, n_splits, partials);
+  if (n_splits > 1)
+    launch_pdl(latent_merge_kernel<T>, dim3(n_rows, n_head), dim3(128), 0, stream, (const float*)partials, out, ldo,
+               rows, row_entry, n_head, kv_rank, n_splits);
   NIB_LAUNCH_CHECK();
 }
 
@@ -210,11 +262,12 @@ template <typename T>
 static int pick_latent_attention(const float* q, const void* cache, void* out, int ldo, const int* block_table,
                                  int max_blocks, const int* rows, const int* row_entry, const int* positions,
                                  int n_rows, int n_head, int kv_rank, int D, int page_size, int n_pages,
-                                 float scale, int window, int* status, cudaStream_t stream) {
+                                 float scale, int window, int* status, int n_splits, float* partials,
+                                 cudaStream_t stream) {
 #define NIB_LA(N)                                                                                              \
   return launch_latent_attention<T, N>(q, (const T*)cache, (T*)out, ldo, block_table, max_blocks, rows,       \
                                        row_entry, positions, n_rows, n_head, kv_rank, D, page_size, n_pages,  \
-                                       scale, window, status, stream)
+                                       scale, window, status, n_splits, partials, stream)
   const int n = (kv_rank + 31) / 32;
   if (n <= 2) NIB_LA(2);
   if (n <= 4) NIB_LA(4);
@@ -269,21 +322,23 @@ extern "C" int nib_rope_heads(int dtype, const void* q, int ldq, int nope, int r
 
 // q: float [T, n_head, D] (absorbed part, then the rotated part), D = kv_rank + rot_dim; cache: one layer
 // [n_pages, page_size, D]; out: [T, n_head * kv_rank] in the cache's dtype.  rows: the step's rows to
-// process (nullptr: rows 0..n_rows-1).
+// process (nullptr: rows 0..n_rows-1).  n_splits > 1: every row's keys are cut into that many pieces, each a
+// block of its own, and merged through `partials` (n_rows * n_head * n_splits * (kv_rank + 2) floats).
 extern "C" int nib_latent_attention(int dtype, const float* q, const void* cache, void* out, int ldo,
                                     const int* block_table, int max_blocks, const int* rows, const int* row_entry,
                                     const int* positions, int n_rows, int n_head, int kv_rank, int D,
-                                    int page_size, int n_pages, float scale, int window, int* status,
-                                    cudaStream_t stream) {
+                                    int page_size, int n_pages, float scale, int window, int* status, int n_splits,
+                                    float* partials, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (kv_rank <= 0 || D < kv_rank || n_head <= 0) return NIB_ERR_BAD_ARGUMENT;
+  if (n_splits < 1 || n_splits > 65535 || (n_splits > 1 && partials == nullptr)) return NIB_ERR_BAD_ARGUMENT;
   if (dtype == DT_F32)
     return pick_latent_attention<float>(q, cache, out, ldo, block_table, max_blocks, rows, row_entry, positions,
                                         n_rows, n_head, kv_rank, D, page_size, n_pages, scale, window, status,
-                                        stream);
+                                        n_splits, partials, stream);
   if (dtype == DT_BF16)
     return pick_latent_attention<bf16>(q, cache, out, ldo, block_table, max_blocks, rows, row_entry, positions,
                                        n_rows, n_head, kv_rank, D, page_size, n_pages, scale, window, status,
-                                       stream);
+                                       n_splits, partials, stream);
   return NIB_ERR_BAD_ARGUMENT;
 }

@@ -83,11 +83,11 @@ _SIGNATURES = {
     "nib_rope_heads": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                        _c_int, _c_int, _c_ptr],
     "nib_latent_attention": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int,
-                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
+                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr],
     "nib_linear_heads": [_c_int, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_int, _c_ptr],
     "nib_delta_rule": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
-                       _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int,
+                       _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int,
                        _c_ptr],
     "nib_moe_route": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "nib_moe_up": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
@@ -988,11 +988,36 @@ def rope_heads(q: torch.Tensor, nope: int, rot_dim: int, rot_dims: int, freqs: t
            "rope_heads")
 
 
+#: blocks of the latent attention that fill the device about twice: a step of few rows cuts every row's keys
+#: into pieces until it has that many blocks (at most LATENT_MAX_SPLITS pieces a row)
+LATENT_BLOCKS, LATENT_MAX_SPLITS, LATENT_HEADS_PER_BLOCK = 296, 16, 8
+
+
+def latent_splits(n_rows: int, n_head: int) -> int:
+    """Into how many pieces the latent attention cuts each row's keys: a function of the step's shape alone
+    (a captured step bakes it in); the pieces' sizes follow from each row's own key range on the device."""
+    groups = -(-n_head // LATENT_HEADS_PER_BLOCK)
+    return max(1, min(LATENT_MAX_SPLITS, LATENT_BLOCKS // max(1, n_rows * groups)))
+
+
+def latent_attention_reserve(workspace, n_head: int, kv_rank: int) -> None:
+    """Scratch of the pieces' partial results: keys are cut only while rows x head groups x pieces stays within
+    LATENT_BLOCKS, which bounds it whatever the step."""
+    workspace.reserve("latent.partials", LATENT_BLOCKS * LATENT_HEADS_PER_BLOCK * (kv_rank + 2), torch.float32)
+
+
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
-                     n_head: int, kv_rank: int, scale: float, window: int) -> None:
+                     n_head: int, kv_rank: int, scale: float, window: int, n_splits: Optional[int] = None) -> None:
     """Causal softmax attention of the step's rows over one latent cache layer: q float32 [T, n_head, D] (the
-    absorbed query, then the rotated part), out [T, n_head * kv_rank] the weighted sums of latents."""
+    absorbed query, then the rotated part), out [T, n_head * kv_rank] the weighted sums of latents.  A step of
+    few rows (decoded tokens) cuts every row's keys into ``n_splits`` pieces, merged by a second kernel."""
     n_pages, _, _, page_size, D = cache.shape
+    if n_splits is None:
+        n_splits = latent_splits(ctx.n_rows, n_head)
+    partials = None
+    if n_splits > 1:
+        need = ctx.n_rows * n_head * n_splits * (kv_rank + 2)
+        partials = ctx.workspace.get("latent.partials", (need,), torch.float32)
     _f32(q, "latent_attention: q")
     if out.dtype != cache.dtype or out.stride(1) != 1 or q.shape[2] != D:
         raise KernelError("latent_attention: out in the cache's dtype, q [T, heads, D]")
@@ -1005,7 +1030,8 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
     _check(library().nib_latent_attention(_dt(cache), _ptr(q), _ptr(cache), _ptr(out), out.stride(0), _ptr(block_table),
                                           block_table.shape[1], None, _ptr(ctx.row_entry), _ptr(ctx.positions),
                                           ctx.n_rows, n_head, kv_rank, D, page_size, n_pages, float(scale),
-                                          int(window), _ptr(ctx.status), _stream()), "latent_attention")
+                                          int(window), _ptr(ctx.status), int(n_splits), _ptr(partials), _stream()),
+           "latent_attention", 2 if n_splits > 1 else 1)
 
 
 def linear_heads(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int,
@@ -1027,7 +1053,8 @@ def delta_rule(proj: torch.Tensor, offsets, wl: torch.Tensor, w0: torch.Tensor, 
                out: torch.Tensor) -> None:
     """The generalised delta rule over the step's entries (csrc/delta_rule.cu).  ``proj`` float32 [T, *] holds
     r, k, v, gate and removal logits at the column ``offsets`` (five), ``wl`` float32 the decay logits; ``state``
-    float32 [slots, n_head, dim, dim] is read and written at the entries' slots."""
+    float32 [slots, n_head, dim, dim] is read and written at the entries' slots.  ``wl`` is scratch afterwards.
+    ``ctx.n_rows`` counts the rows of the entries only where rows of no request follow them."""
     _f32(proj, "delta_rule: proj"); _f32(state, "delta_rule: state")
     if wl.dtype != torch.float32 or wl.stride(1) != 1 or out.stride(1) != 1 or tuple(state.shape[1:]) != (n_head, dim, dim):
         raise KernelError("delta_rule: wl float32, state [slots, heads, dim, dim]")
@@ -1038,8 +1065,8 @@ def delta_rule(proj: torch.Tensor, offsets, wl: torch.Tensor, w0: torch.Tensor, 
               T * n_head * dim * (6 * 4 + out.element_size()) + 8.0 * ctx.n_entries * n_head * dim * dim)
     _check(library().nib_delta_rule(_dt(out), _ptr(proj), proj.stride(0), r_off, k_off, v_off, g_off, a_off, _ptr(wl),
                                     wl.stride(0), _ptr(w0), _ptr(a_bias), _ptr(norm_w), _ptr(state),
-                                    _ptr(ctx.entry_start), _ptr(ctx.entry_slot), ctx.n_entries, n_head, dim,
-                                    float(eps), _ptr(out), out.stride(0), _stream()), "delta_rule")
+                                    _ptr(ctx.entry_start), _ptr(ctx.entry_slot), ctx.n_entries, ctx.n_rows, n_head,
+                                    dim, float(eps), _ptr(out), out.stride(0), _stream()), "delta_rule")
 
 
 # ------------------------------------------------------------------------------ routed experts
@@ -1065,7 +1092,7 @@ def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, inner: torch.
             or inner.shape[1] != F:
         raise KernelError("moe_up: h, w_up and inner share a dtype; inner contiguous [T * top, F]")
     if tracing():
-        _note("matmul", "experts_up", (T * top, C, F), 2.0 * T * top * C * F,
+        _note("moe", "experts_up", (T * top, C, F), 2.0 * T * top * C * F,
               h.element_size() * (min(E, T * top) * F * C + T * C + T * top * F))
     _check(library().nib_moe_up(_dt(h), _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), _ptr(inner), T, C, F, top,
                                 int(act), _stream()), "moe_up")
@@ -1079,7 +1106,7 @@ def moe_down(inner: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weigh
     if inner.dtype != w_down.dtype or not w_down.is_contiguous() or not inner.is_contiguous() or x.shape[1] != C:
         raise KernelError("moe_down: inner and w_down share a dtype; x [T, C]")
     if tracing():
-        _note("matmul", "experts_down", (T * top, F, C), 2.0 * T * top * C * F,
+        _note("moe", "experts_down", (T * top, F, C), 2.0 * T * top * C * F,
               inner.element_size() * (min(E, T * top) * F * C + T * top * F) + 8.0 * T * C)
     _check(library().nib_moe_down(_dt(inner), _ptr(inner), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(x), T, C, F,
                                   top, _stream()), "moe_down")

@@ -84,6 +84,7 @@ class LatentAttention(Mixer):
         workspace.reserve("latent.q_full", n * H * self.latent_dim, torch.float32)
         workspace.reserve("latent.out", n * H * self.kv_rank, self.dtype)
         workspace.reserve("latent.att", n * H * self.v_dim, self.dtype)
+        ops.latent_attention_reserve(workspace, H, self.kv_rank)
 
     def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: Optional[KVCacheView],
                 state: Optional[torch.Tensor], writes_cache: bool = True) -> None:

@@ -125,14 +125,16 @@ def dense_ff(h, W, p: str) -> torch.Tensor:
 def routed_ff(h, W, p: str, mlp: dict, margins: Optional[torch.Tensor] = None) -> torch.Tensor:
     """softmax over all experts of the router's logits, the ``top`` largest chosen, weighted by their
     scores as they are; a shared expert, if any, is added for every row.  ``margins`` [n] (optional) is
-    lowered to each row's relative gap between the last score chosen and the first one left out: a test
-    of a reduced-precision engine leaves out rows whose choice is that close a call."""
+    lowered to each row's relative gap between the last score chosen and the first one left out (where that
+    last score weighs anything: a choice between two experts that both count for less than 0.002 is no
+    call at all): a test of a reduced-precision engine leaves out rows whose choice is that close a call."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     s = torch.softmax(h @ W[p + "router"].T, dim=-1)
     score, chosen = torch.topk(s, top, dim=-1)
     if margins is not None and top < E:
         ranked = torch.sort(s, dim=-1, descending=True).values
-        torch.minimum(margins, (ranked[:, top - 1] - ranked[:, top]) / ranked[:, top - 1], out=margins)
+        gap = (ranked[:, top - 1] - ranked[:, top]) / ranked[:, top - 1]
+        torch.minimum(margins, torch.where(ranked[:, top - 1] < 2e-3, torch.ones_like(gap), gap), out=margins)
     out = torch.zeros_like(h)
     for e in range(E):
         hit = chosen == e

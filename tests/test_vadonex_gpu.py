@@ -130,7 +130,7 @@ def test_routing_kernels_against_torch(E, top, C, F, dtype):
     assert float((x[:T] - (x0[:T] + add)).abs().max()) < 1e-4 and torch.equal(x[T:], x0[T:])
 
 
-@pytest.mark.parametrize("dim", [16, 40, 64])
+@pytest.mark.parametrize("dim", [16, 40, 48, 64, 128])
 def test_delta_rule_kernel_carries_its_state_in_the_slot(dim):
     from nanoinfer_b200.kernels import ops
 
@@ -194,7 +194,7 @@ def test_delta_rule_kernel_carries_its_state_in_the_slot(dim):
         assert float((state - want_state).abs().max()) < 2e-4, cuts      # untouched slots stay as they were
 
 
-def _latent_case(dtype, kv_rank, rot, page, window, positions, hot):
+def _latent_case(dtype, kv_rank, rot, page, window, positions, hot, n_splits=None):
     """One request's rows at ``positions`` over a cache whose pages lie in a scrambled order; the key at
     ``hot[i]`` is made to tower over row i's other scores."""
     from nanoinfer_b200.kernels import ops
@@ -215,12 +215,14 @@ def _latent_case(dtype, kv_rank, rot, page, window, positions, hot):
     for j in range(n_keys):
         cache[int(table[j // page]), 0, 0, j % page] = lat[j].to(DEV)
     T = len(positions) + 1                                      # the last row belongs to no request
-    ctx = SimpleNamespace(n_rows=T, row_entry=torch.tensor([0] * (T - 1) + [-1], dtype=torch.int32, device=DEV),
+    from nanoinfer_b200.parts.base import Workspace
+    ctx = SimpleNamespace(n_rows=T, workspace=Workspace(torch.device(DEV)),
+                          row_entry=torch.tensor([0] * (T - 1) + [-1], dtype=torch.int32, device=DEV),
                           positions=torch.tensor(list(positions) + [0], dtype=torch.int32, device=DEV),
                           status=torch.zeros(1, dtype=torch.int32, device=DEV), host_entry_pos0=[], host_entry_start=[0])
     out = torch.full((T, H * kv_rank), 7.0, device=DEV, dtype=dtype)
     ops.latent_attention(q.to(DEV), cache[:, :, :, :, :], out, table.view(1, -1).to(DEV).contiguous(), ctx, H, kv_rank,
-                         0.8, window)
+                         0.8, window, n_splits=n_splits)
     assert int(ctx.status) == 0 and (out[-1] == 7.0).all()
     ref, weight_on_hot = [], []
     for i, p in enumerate(positions):
@@ -234,20 +236,21 @@ def _latent_case(dtype, kv_rank, rot, page, window, positions, hot):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_splits", [1, 3, None])      # the keys whole, in three pieces, and as a step of few rows cuts them
 @pytest.mark.parametrize("kv_rank,rot,page,window", [(32, 8, 16, 24), (20, 6, 16, 17), (96, 32, 32, 40), (40, 0, 16, 0),
-                                                      (64, 16, 16, 1)])
-def test_latent_attention_kernel_at_the_windows_edges(kv_rank, rot, page, window, dtype):
+                                                      (64, 16, 16, 1), (48, 16, 16, 100)])
+def test_latent_attention_kernel_at_the_windows_edges(kv_rank, rot, page, window, n_splits, dtype):
     w = window or 1000
     positions = [0, 1, page - 1, page, w - 1, w, w + 1, 3 * page + 5, 130, 131]
     # a towering key just inside the window (the last one it keeps), just outside it, and at the row itself
     inside = [max(0, p - w + 1) for p in positions]
-    got, ref, hot_w = _latent_case(DT[dtype], kv_rank, rot, page, window, positions, inside)
+    got, ref, hot_w = _latent_case(DT[dtype], kv_rank, rot, page, window, positions, inside, n_splits)
     tol = 2e-5 if dtype == "float32" else 0.03
     assert float((got - ref).abs().max()) < tol
     if window != 1:
         assert min(x for x in hot_w if x is not None) > 0.5          # the edge key carries the row: losing it would show
     outside = [p - w if p - w >= 0 else None for p in positions]
-    got, ref, _ = _latent_case(DT[dtype], kv_rank, rot, page, window, positions, outside)
+    got, ref, _ = _latent_case(DT[dtype], kv_rank, rot, page, window, positions, outside, n_splits)
     assert float((got - ref).abs().max()) < tol                      # a key one behind the window must weigh nothing
 
 

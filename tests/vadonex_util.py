@@ -104,10 +104,9 @@ CLOSE_CALL = 0.03
 
 
 def clear_rows(plain, dtype) -> torch.Tensor:
-    """After ``plain.logits(tokens)``: which positions a comparison in ``dtype`` may rest on.  A close call at
-    one position changes what later positions see through the state and the cache, so the positions after
-    it are left out with it where the model has mixers (it always has)."""
+    """After ``plain.logits(tokens)``: which positions a comparison in ``dtype`` may rest on: in bfloat16 all
+    but those at which some router of the plain model made a close call (what a flipped choice at one
+    position does to later ones through the cache and the state stays far below the bound)."""
     if dtype == "float32":
         return torch.ones_like(plain.router_margin, dtype=torch.bool)
-    close = plain.router_margin < CLOSE_CALL
-    return ~(torch.cumsum(close.to(torch.int64), 0) > 0)
+    return plain.router_margin >= CLOSE_CALL
