@@ -8,6 +8,13 @@
 //               an output, so the sum has a fixed order and needs no atomics)
 // Expert weights are stacked [n_expert, out, in].  A warp makes an output at a time: its lanes walk the
 // input dimension, which is how the weight rows lie in memory.  Accumulation and activation are 32-bit.
+//
+// These three read an expert's weights again for every row that visits it, which is right for a handful of
+// rows.  A step of many rows turns the loop inside out (moe_grouped): a block owns (expert, 32 outputs), keeps
+// that tile of the expert's matrix in shared memory, and streams through it every row that chose the expert
+// (each warp scans the step's choices for its own share of them; a lane per output, the row broadcast from
+// shared memory).  The second product leaves each (row, choice)'s weighted result in a buffer of its own and
+// moe_combine adds a row's choices into the stream in the order of the choices: no atomics, a fixed order.
 #include "api.h"
 #include "common.cuh"
 
@@ -120,9 +127,141 @@ moe_down_kernel(const T* inner, const T* __restrict__ w_down, const int* ids, co
   }
 }
 
+constexpr int MOE_G_WARPS = 4, MOE_G_OUT = 32, MOE_G_ROWS = 4;
+
+// MODE 0: out[p, n] = act(W[e][n] . src[p / top])   (src: the rows, out: T [P, N])
+// MODE 1: out[p, n] = weights[p] * (W[e][n] . src[p])   (src: the inner activations [P, K], out: float [P, N])
+// A warp collects four (row, choice) pairs of the block's expert at a time and lays their inputs side by side
+// ([K][4] floats), so that one 16-byte read serves four multiply-adds beside one read of the lane's weight.
+template <typename T, typename TO, int MODE>
+__global__ void __launch_bounds__(MOE_G_WARPS * 32)
+moe_grouped_kernel(const T* src, int ld_src, const T* __restrict__ w, const int* ids, const float* weights, TO* out,
+                   int n_pairs, int top, int N, int K, int kp, int act) {
+  pdl_trigger();
+  extern __shared__ __align__(16) unsigned char raw[];
+  float4* rows = reinterpret_cast<float4*>(raw);                            // [warps][K]: four inputs side by side
+  T* wt = reinterpret_cast<T*>(raw + (size_t)MOE_G_WARPS * K * sizeof(float4));   // [MOE_G_OUT][kp]: the expert's tile
+  const int e = blockIdx.x, n0 = blockIdx.y * MOE_G_OUT;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* we = w + ((size_t)e * N + n0) * K;
+  for (int n = warp; n < MOE_G_OUT; n += MOE_G_WARPS)
+    for (int k = lane; k < K; k += 32) wt[n * kp + k] = n0 + n < N ? we[(size_t)n * K + k] : from_float<T>(0.0f);
+  pdl_wait();
+  __syncthreads();
+  float4* row = rows + warp * K;
+  const T* mine = wt + lane * kp;
+  int found[MOE_G_ROWS], nf = 0;
+  auto run = [&]() {                      // the products of the nf pairs in `found` with the block's tile
+    const T* s[MOE_G_ROWS];
+#pragma unroll
+    for (int i = 0; i < MOE_G_ROWS; ++i) s[i] = src + (size_t)(i < nf ? (MODE == 0 ? found[i] / top : found[i]) : 0) * ld_src;
+    __syncwarp();
+#pragma unroll 4
+    for (int k = lane; k < K; k += 32)
+      row[k] = make_float4(to_float(s[0][k]), nf > 1 ? to_float(s[1][k]) : 0.f, nf > 2 ? to_float(s[2][k]) : 0.f,
+                           nf > 3 ? to_float(s[3][k]) : 0.f);
+    __syncwarp();
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int k = 0; k < K; ++k) {
+      const float wv = to_float(mine[k]);
+      const float4 a = row[k];
+      acc.x += a.x * wv; acc.y += a.y * wv; acc.z += a.z * wv; acc.w += a.w * wv;
+    }
+    const float v[MOE_G_ROWS] = {acc.x, acc.y, acc.z, acc.w};
+    if (n0 + lane < N) {
+#pragma unroll
+      for (int i = 0; i < MOE_G_ROWS; ++i) {
+        if (i < nf) {
+          if (MODE == 0)
+            out[(size_t)found[i] * N + n0 + lane] = from_float<TO>(apply_act(v[i], act));
+          else
+            out[(size_t)found[i] * N + n0 + lane] = from_float<TO>(weights[found[i]] * v[i]);
+        }
+      }
+    }
+    nf = 0;
+  };
+  // a warp looks at 32 choices at a time (a lane each) and takes those of the block's expert in their order
+  for (int base = warp * 32; base < n_pairs; base += MOE_G_WARPS * 32) {
+    const int p = base + lane;
+    unsigned hits = __ballot_sync(0xffffffffu, p < n_pairs && ids[p] == e);
+    while (hits) {
+      const int bit = __ffs(hits) - 1;
+      hits &= hits - 1;
+#pragma unroll
+      for (int i = 0; i < MOE_G_ROWS; ++i)
+        if (i == nf) found[i] = base + bit;
+      if (++nf == MOE_G_ROWS) run();
+    }
+  }
+  if (nf > 0) run();
+}
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* parts, float* x, int C, int top, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t t = i / C, c = i % C;
+  float total = 0.0f;
+  for (int k = 0; k < top; ++k) total += parts[(t * top + k) * C + c];
+  x[i] += total;
+}
+
+// the padded row length of the staged tile: lanes read rows `kp` elements apart, which must fall into 32 different banks
+template <typename T> static int moe_padded(int K) {
+  if (sizeof(T) == 4) return K | 1;
+  int kp = K + (K & 1);            // even
+  return (kp / 2) % 2 ? kp : kp + 2;
+}
+template <typename T> static size_t moe_grouped_smem(int K) {
+  return (size_t)MOE_G_OUT * moe_padded<T>(K) * sizeof(T) + (size_t)MOE_G_WARPS * K * sizeof(float4);
+}
+
+template <typename T, typename TO, int MODE>
+static int launch_moe_grouped(const T* src, int ld_src, const T* w, const int* ids, const float* weights, TO* out,
+                              int n_pairs, int top, int n_expert, int N, int K, int act, cudaStream_t stream) {
+  const size_t smem = moe_grouped_smem<T>(K);
+  if (smem > 200 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(moe_grouped_kernel<T, TO, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  launch_pdl(moe_grouped_kernel<T, TO, MODE>, dim3(n_expert, (N + MOE_G_OUT - 1) / MOE_G_OUT), dim3(MOE_G_WARPS * 32),
+             smem, stream, src, ld_src, w, ids, weights, out, n_pairs, top, N, K, moe_padded<T>(K), act);
+  NIB_LAUNCH_CHECK();
+}
+
 }  // namespace nib
 
 using namespace nib;
+
+// The expert-major form of nib_moe_up (phase 0), nib_moe_down into `parts` float [T * top, C] (phase 1), and the sum of
+// a row's parts into the stream (phase 2).  -2 where a tile of an expert's matrix does not fit shared memory.
+extern "C" int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src, const void* w, const int* ids,
+                               const float* weights, void* out, float* x, int T, int top, int n_expert, int N, int K,
+                               int act, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (phase == 2) {
+    const size_t n = (size_t)T * N;
+    launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)src, x, N, top, n);
+    NIB_LAUNCH_CHECK();
+  }
+  if (dtype == DT_F32) {
+    if (phase == 0)
+      return launch_moe_grouped<float, float, 0>((const float*)src, ld_src, (const float*)w, ids, weights, (float*)out,
+                                                 T * top, top, n_expert, N, K, act, stream);
+    return launch_moe_grouped<float, float, 1>((const float*)src, ld_src, (const float*)w, ids, weights, (float*)out,
+                                               T * top, top, n_expert, N, K, act, stream);
+  }
+  if (dtype == DT_BF16) {
+    if (phase == 0)
+      return launch_moe_grouped<bf16, bf16, 0>((const bf16*)src, ld_src, (const bf16*)w, ids, weights, (bf16*)out,
+                                               T * top, top, n_expert, N, K, act, stream);
+    return launch_moe_grouped<bf16, float, 1>((const bf16*)src, ld_src, (const bf16*)w, ids, weights, (float*)out,
+                                              T * top, top, n_expert, N, K, act, stream);
+  }
+  return NIB_ERR_BAD_ARGUMENT;
+}
 
 extern "C" int nib_moe_route(int dtype, const void* h, int ldh, const void* w_router, int T, int C, int n_expert,
                              int top, int renorm, int* ids, float* weights, cudaStream_t stream) {

@@ -92,6 +92,8 @@ _SIGNATURES = {
     "nib_moe_route": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "nib_moe_up": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_down": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "nib_moe_grouped": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                        _c_int, _c_int, _c_int, _c_ptr],
 }
 
 
@@ -1110,3 +1112,43 @@ def moe_down(inner: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weigh
               inner.element_size() * (min(E, T * top) * F * C + T * top * F) + 8.0 * T * C)
     _check(library().nib_moe_down(_dt(inner), _ptr(inner), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(x), T, C, F,
                                   top, _stream()), "moe_down")
+
+
+#: rows per expert (on average) from which the routed feed-forward runs expert by expert, each tile of an
+#: expert's matrix staged once, instead of row by row
+MOE_GROUPED_MIN_ROWS_PER_EXPERT = 8
+MOE_GROUPED = True
+
+
+def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                inner: torch.Tensor, x: torch.Tensor, T: int, top: int, act: int, workspace) -> None:
+    """x[t] += sum_k weights[t, k] * w_down[ids[t, k]] . act(w_up[ids[t, k]] . h[t]): row by row for steps of few
+    rows, expert by expert (weights staged in shared memory, a fixed order of additions) for steps of many."""
+    E, F, C = w_up.shape
+    es = h.element_size()
+    fits = all(32 * (K + 2) * es + 4 * K * 16 <= 200 * 1024 for K in (C, F))   # a tile of 32 outputs, four rows a warp
+    grouped = MOE_GROUPED and T * top >= MOE_GROUPED_MIN_ROWS_PER_EXPERT * E and fits
+    if not grouped:
+        moe_up(h, w_up, ids, inner, T, top, act)
+        moe_down(inner, w_down, ids, weights, x, T, top)
+        return
+    _f32(x, "moe_experts: x")
+    if h.dtype != w_up.dtype or inner.dtype != h.dtype or not w_up.is_contiguous() or not w_down.is_contiguous() \
+            or not inner.is_contiguous() or h.stride(1) != 1:
+        raise KernelError("moe_experts: h, the experts and inner share a dtype, contiguous")
+    lib, dt = library(), _dt(h)
+    if tracing():
+        _note("moe", "experts_up", (T * top, C, F), 2.0 * T * top * C * F,
+              h.element_size() * (min(E, T * top) * F * C + T * C + T * top * F))
+    _check(lib.nib_moe_grouped(dt, 0, _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), None, _ptr(inner), None, T, top, E,
+                               F, C, int(act), _stream()), "moe_grouped up")
+    parts = workspace.get("moe.parts", (T * top, C), torch.float32)
+    if tracing():
+        _note("moe", "experts_down", (T * top, F, C), 2.0 * T * top * C * F,
+              h.element_size() * (min(E, T * top) * F * C + T * top * F) + 4.0 * T * top * C)
+    _check(lib.nib_moe_grouped(dt, 1, _ptr(inner), inner.stride(0), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(parts),
+                               None, T, top, E, C, F, 0, _stream()), "moe_grouped down")
+    if tracing():
+        _note("other", "experts_sum", (T, C, top), T * C * top, 4.0 * T * C * (top + 2))
+    _check(lib.nib_moe_grouped(dt, 2, _ptr(parts), 0, None, None, None, None, _ptr(x), T, top, E, C, F, 0, _stream()),
+           "moe_grouped sum")

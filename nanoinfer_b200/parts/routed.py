@@ -59,6 +59,7 @@ class RoutedExperts(FeedForward):
         workspace.reserve("moe.ids", n * self.top, torch.int32)
         workspace.reserve("moe.weights", n * self.top, torch.float32)
         workspace.reserve("moe.inner", n * self.top * self.inner, self.dtype)
+        workspace.reserve("moe.parts", n * self.top * self.width, torch.float32)
         if self.shared_inner:
             workspace.reserve("moe.shared", n * self.shared_inner, self.dtype)
 
@@ -72,8 +73,8 @@ class RoutedExperts(FeedForward):
         ops.moe_route(xn, p["router"], T, self.top, self.renorm, ids, weights)
         inner = ws.get("moe.inner", (n * self.top, self.inner), self.dtype)
         ops.trace_scope(ctx.layer, "experts")
-        ops.moe_up(xn, self.w_up, ids, inner, T, self.top, ops.ACT_CODES[self.activation])
-        ops.moe_down(inner, self.w_down, ids, weights, x, T, self.top)
+        ops.moe_experts(xn, self.w_up, self.w_down, ids, weights, inner, x, T, self.top,
+                        ops.ACT_CODES[self.activation], ws)
         if self.shared_inner:
             hs = ws.get("moe.shared", (n, self.shared_inner), self.dtype)
             ops.trace_scope(ctx.layer, "shared_fc")

@@ -130,6 +130,37 @@ def test_routing_kernels_against_torch(E, top, C, F, dtype):
     assert float((x[:T] - (x0[:T] + add)).abs().max()) < 1e-4 and torch.equal(x[T:], x0[T:])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("E,top,C,F", [(4, 2, 72, 50), (3, 1, 130, 33), (8, 3, 256, 96)])
+def test_experts_row_by_row_and_expert_by_expert_agree(E, top, C, F, dtype):
+    from nanoinfer_b200.kernels import ops
+    from nanoinfer_b200.parts.base import Workspace
+
+    torch.manual_seed(E + C)
+    dt, T = DT[dtype], 150
+    h = torch.randn(T, C, device=DEV).to(dt)
+    up, down = (torch.randn(E, F, C, device=DEV) * 0.2).to(dt), (torch.randn(E, C, F, device=DEV) * 0.2).to(dt)
+    ids = torch.stack([torch.randperm(E)[:top] for _ in range(T)]).to(torch.int32).to(DEV)
+    wts = torch.rand(T, top, device=DEV)
+    x0 = torch.randn(T, C, device=DEV)
+    got = {}
+    for grouped in (False, True):
+        ops.MOE_GROUPED = grouped
+        try:
+            x, inner = x0.clone(), torch.zeros(T * top, F, device=DEV, dtype=dt)
+            ops.moe_experts(h, up, down, ids, wts, inner, x, T, top, ops.ACT_GELU_ERF, Workspace(torch.device(DEV)))
+            got[grouped] = (x, inner)
+        finally:
+            ops.MOE_GROUPED = True
+    pre = torch.einsum("tc,tkfc->tkf", h.double(), up.double()[ids.long()])
+    mid = (0.5 * pre * (1 + torch.erf(pre / math.sqrt(2)))).to(dt).double()
+    want = x0.double() + torch.einsum("tk,tkf,tkcf->tc", wts.double(), mid, down.double()[ids.long()])
+    tol = 1e-4 if dtype == "float32" else 0.05
+    for grouped, (x, inner) in got.items():
+        assert float((x - want).abs().max()) < tol, grouped
+    assert float((got[True][0] - got[False][0]).abs().max()) < tol / 10 + 1e-5
+
+
 @pytest.mark.parametrize("dim", [16, 40, 48, 64, 128])
 def test_delta_rule_kernel_carries_its_state_in_the_slot(dim):
     from nanoinfer_b200.kernels import ops
