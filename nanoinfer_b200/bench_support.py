@@ -383,6 +383,14 @@ def print_profile(eng, prompt, out=None) -> None:
 
     out = out or sys.stderr
     peaks = measured_peaks()
+    if not eng.cache.can_truncate:
+        # a model with mixer state or windows: every repeat runs on requests of its own (no sampler's launch)
+        pre, dec = profile_forward(eng, list(prompt), 1)
+        print(trace.format_table(pre, peaks["hbm_gbs"], peaks["bf16_tflops"],
+                                 f"\nprefill of {len(prompt)} tokens (kernels launched one by one; peaks {peaks['source']})"), file=out)
+        print(trace.format_table(dec, peaks["hbm_gbs"], peaks["bf16_tflops"],
+                                 f"\none decode step behind {len(prompt) + 1} tokens"), file=out)
+        return
     r = eng.cache.open_request()
     eng.sampler.set_request(r.slot, SamplingParams(temperature=0.0))
     pre = profile_step(eng, [StepItem(r, list(prompt), [len(prompt) - 1])], eng.sampler, phase="prefill")

@@ -313,6 +313,11 @@ class CacheManager:
                         blocks[b] = -1
                         row[b] = -1
 
+    @property
+    def can_truncate(self) -> bool:
+        """Whether a request can be cut back at all: not with per-request mixer state, not behind a window."""
+        return not self._state_keys and all(g.spec.window <= 0 for g in self.groups)
+
     def truncate(self, req: RequestCache, n_tokens: int) -> None:
         """Forget positions from ``n_tokens`` on; pages wholly past it go back
         (crates/metal/src/batch.rs:220-227).  Not possible behind a window or with mixer state."""

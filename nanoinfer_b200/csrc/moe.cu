@@ -15,6 +15,8 @@
 // (each warp scans the step's choices for its own share of them; a lane per output, the row broadcast from
 // shared memory).  The second product leaves each (row, choice)'s weighted result in a buffer of its own and
 // moe_combine adds a row's choices into the stream in the order of the choices: no atomics, a fixed order.
+#include <algorithm>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -136,7 +138,7 @@ constexpr int MOE_G_WARPS = 4, MOE_G_OUT = 32, MOE_G_ROWS = 4;
 template <typename T, typename TO, int MODE>
 __global__ void __launch_bounds__(MOE_G_WARPS * 32)
 moe_grouped_kernel(const T* src, int ld_src, const T* __restrict__ w, const int* ids, const float* weights, TO* out,
-                   int n_pairs, int top, int N, int K, int kp, int act) {
+                   int n_pairs, int top, int N, int K, int kp, int act, int chunk) {
   pdl_trigger();
   extern __shared__ __align__(16) unsigned char raw[];
   float4* rows = reinterpret_cast<float4*>(raw);                            // [warps][K]: four inputs side by side
@@ -182,10 +184,13 @@ moe_grouped_kernel(const T* src, int ld_src, const T* __restrict__ w, const int*
     }
     nf = 0;
   };
-  // a warp looks at 32 choices at a time (a lane each) and takes those of the block's expert in their order
-  for (int base = warp * 32; base < n_pairs; base += MOE_G_WARPS * 32) {
+  // a warp looks at 32 choices at a time (a lane each) and takes those of the block's expert in their order;
+  // the step's choices are cut into gridDim.z chunks, a block a chunk, so that an expert that many rows chose
+  // is the work of many blocks
+  const int last = min(n_pairs, ((int)blockIdx.z + 1) * chunk);
+  for (int base = blockIdx.z * chunk + warp * 32; base < last; base += MOE_G_WARPS * 32) {
     const int p = base + lane;
-    unsigned hits = __ballot_sync(0xffffffffu, p < n_pairs && ids[p] == e);
+    unsigned hits = __ballot_sync(0xffffffffu, p < last && ids[p] == e);
     while (hits) {
       const int bit = __ffs(hits) - 1;
       hits &= hits - 1;
@@ -226,8 +231,12 @@ static int launch_moe_grouped(const T* src, int ld_src, const T* w, const int* i
   if (smem > 200 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(moe_grouped_kernel<T, TO, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  launch_pdl(moe_grouped_kernel<T, TO, MODE>, dim3(n_expert, (N + MOE_G_OUT - 1) / MOE_G_OUT), dim3(MOE_G_WARPS * 32),
-             smem, stream, src, ld_src, w, ids, weights, out, n_pairs, top, N, K, moe_padded<T>(K), act);
+  // chunks of the choices: about 32 choices of the block's expert a block if the choices were even
+  const int z = std::max(1, std::min(64, n_pairs / (32 * n_expert)));
+  const int chunk = ((n_pairs + z - 1) / z + 31) / 32 * 32;
+  launch_pdl(moe_grouped_kernel<T, TO, MODE>, dim3(n_expert, (N + MOE_G_OUT - 1) / MOE_G_OUT, (n_pairs + chunk - 1) / chunk),
+             dim3(MOE_G_WARPS * 32), smem, stream, src, ld_src, w, ids, weights, out, n_pairs, top, N, K,
+             moe_padded<T>(K), act, chunk);
   NIB_LAUNCH_CHECK();
 }
 

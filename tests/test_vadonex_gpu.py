@@ -628,3 +628,22 @@ def test_trace_replay_of_a_model_folder(tmp_path):
     s.close()
     for r, t in reqs.items():
         assert rel_err(s.stacked(r, len(t)), plain.logits(t)) <= TOL["float32"], r
+
+
+def test_command_line_writes_a_folder_generates_from_it_and_profiles(tmp_path, capsys):
+    """The command line as for the other architecture: random-weights from the preset, generate (the tokens
+    of the entry point, which are the plain model's), and the per-op profile of a prefill and a decode step."""
+    import nanoinfer_b200 as nb
+    from nanoinfer_b200 import cli
+    from plain_vadonex import PlainVadonex
+
+    d = str(tmp_path / "m")
+    assert cli.main(["random-weights", "--config", "vadonex-tiny", "--seed", "6", "--out", d, "--dtype", "float32"]) == 0
+    capsys.readouterr()
+    prompt = toks(512, 12, 77)
+    assert cli.main(["--weights", d, "generate", "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+                     "--tokens", "10", "--temperature", "0.0", "--profile"]) == 0
+    captured = capsys.readouterr()
+    printed = [int(t) for t in captured.out.split()]
+    assert printed == PlainVadonex(d).greedy(prompt, 10)
+    assert "delta_rule" in captured.err and "attn" in captured.err and "experts_up" in captured.err
