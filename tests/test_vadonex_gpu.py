@@ -25,7 +25,7 @@ def toks(vocab, n, seed):
 
 
 # =============================================================================== kernels alone
-@pytest.mark.parametrize("C", [40, 320, 1536])
+@pytest.mark.parametrize("C", [40, 264, 1536])
 def test_stream_kernels_against_torch(C):
     from nanoinfer_b200.kernels import ops
 
@@ -97,7 +97,7 @@ def test_product_per_head_against_torch(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("E,top,C,F", [(5, 1, 40, 12), (4, 4, 64, 33), (16, 3, 96, 24)])
+@pytest.mark.parametrize("E,top,C,F", [(5, 1, 40, 12), (4, 4, 64, 33), (12, 3, 88, 24)])
 def test_routing_kernels_against_torch(E, top, C, F, dtype):
     from nanoinfer_b200.kernels import ops
 
@@ -268,7 +268,7 @@ def _latent_case(dtype, kv_rank, rot, page, window, positions, hot, n_splits=Non
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n_splits", [1, 3, None])      # the keys whole, in three pieces, and as a step of few rows cuts them
-@pytest.mark.parametrize("kv_rank,rot,page,window", [(32, 8, 16, 24), (20, 6, 16, 17), (96, 32, 32, 40), (40, 0, 16, 0),
+@pytest.mark.parametrize("kv_rank,rot,page,window", [(32, 8, 16, 24), (20, 6, 16, 17), (80, 24, 32, 36), (40, 0, 16, 0),
                                                       (64, 16, 16, 1), (48, 16, 16, 100)])
 def test_latent_attention_kernel_at_the_windows_edges(kv_rank, rot, page, window, n_splits, dtype):
     w = window or 1000
