@@ -168,10 +168,10 @@ int nib_linear_heads(int dtype, int out_dtype, const void* a, int lda, int a_hea
                      int ldo, int out_head_stride, int M, int n_head, int N, int K, cudaStream_t stream);
 
 // ---- the generalised delta rule (delta_rule.cu)
-int nib_delta_rule(int dtype, const float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off,
+int nib_delta_rule(int dtype, float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off,
                    float* wl, int ld_w, const float* w0, const float* a_bias, const float* norm_w,
                    float* state, const int* entry_start, const int* entry_slot, int n_entries, int n_rows, int n_head,
-                   int dim, float eps, void* out, int ldo, cudaStream_t stream);
+                   int dim, float eps, void* out, int ldo, float* unit, cudaStream_t stream);
 
 // ---- a routed feed-forward (moe.cu)
 int nib_moe_route(int dtype, const void* h, int ldh, const void* w_router, int T, int C, int n_expert, int top,

@@ -7,9 +7,10 @@
 //   S_t = diag(w) S_(t-1) - (a * u) (u^T S_(t-1)) + k v^T        (both terms read the old state)
 //   o_t = S_t^T r
 // then each head's o is divided by its root mean square, multiplied by a weight and by sigmoid(gate).
-// One block per (batch entry, head) walks the entry's rows in order; thread j owns value channel j (a column
-// of S: the columns do not see one another).  For head sizes that are multiples of 16 up to 128 the column
-// lives in the thread's registers, every token's per-channel vectors (r, k, w, a u, u) are made by the
+// One block per (batch entry, head) walks the entry's rows in order; a column of S belongs to one value
+// channel, and the columns do not see one another.  For head sizes that are multiples of 16 up to 128 a
+// column lives in the registers of four neighbouring threads, a quarter of the key channels each (u^T S and
+// S^T r are then sums over four lanes: two shuffles), every token's per-channel vectors (r, k, w, a u, u) are made by the
 // channel's thread for the NEXT token while this one is worked on and passed through a double buffer in
 // shared memory (one barrier a token), the raw outputs take the place of the decay logits already used, and
 // the division by each head's root mean square is a pass over the rows afterwards (inside the kernel for a
@@ -88,8 +89,36 @@ __global__ void delta_rule_kernel(const float* proj, int ld, int r_off, int k_of
 }
 
 template <int DIM> struct DeltaInputs {
-  float r, k, a, w, v, ks[(DIM + 31) / 32];
+  float r, k, a, w, u, v, ks[(DIM + 31) / 32];
 };
+
+// What a token gives the recurrence besides r, k and v does not depend on the state: for a step with prompt
+// portions it is made for all rows at once, a warp a (row, head): the decay w takes the place of its logit, a u
+// the place of the removal logit, the unit key u goes to a buffer of its own.
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(float* proj, int ld, int k_off, int a_off, float* wl, int ld_w, const float* __restrict__ w0,
+                     const float* __restrict__ a_bias, float* unit, int n_head, int dim, int n_rows) {
+  pdl_trigger();
+  const int wi = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  pdl_wait();
+  if (wi >= n_rows * n_head) return;
+  const int t = wi / n_head, h = wi % n_head;
+  float* p = proj + (size_t)t * ld;
+  float ks = 0.0f;
+  for (int i = lane; i < dim; i += 32) {
+    const float k = p[k_off + h * dim + i];
+    ks += k * k;
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(ks) + 1e-6f);
+  for (int i = lane; i < dim; i += 32) {
+    const int col = h * dim + i;
+    const float u = p[k_off + col] * inv;
+    const size_t at = (size_t)t * ld_w + col;
+    wl[at] = expf(-0.6065306597126334f * sigmoid_f(wl[at] + w0[col]));
+    p[a_off + col] = sigmoid_f(p[a_off + col] + a_bias[col]) * u;
+    unit[(size_t)t * n_head * dim + col] = u;
+  }
+}
 
 // o[t, head] / rms * weight * sigmoid(gate) for the rows t = first, first + step, ... below `end`; a warp a row.
 template <typename T, int DIM>
@@ -118,50 +147,73 @@ __device__ __forceinline__ void delta_finish_rows(const float* proj, int ld, int
   }
 }
 
+constexpr int DELTA_PARTS = 4;     // threads that share a column of the state, each a quarter of the key channels
+
 template <typename T, int DIM>
-__global__ void __launch_bounds__((DIM + 31) / 32 * 32)
+__global__ void __launch_bounds__(DIM * DELTA_PARTS)
 delta_rule_reg_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off, float* wl,
                       int ld_w, const float* __restrict__ w0, const float* __restrict__ a_bias,
                       const float* __restrict__ norm_w, float* state, const int* __restrict__ entry_start,
-                      const int* __restrict__ entry_slot, int n_head, float eps, T* out, int ldo, int finish_inside) {
+                      const int* __restrict__ entry_slot, int n_head, float eps, T* out, int ldo, int finish_inside,
+                      const float* unit) {
   pdl_trigger();
-  constexpr int NT = (DIM + 31) / 32 * 32, M = (DIM + 31) / 32;
+  constexpr int KPT = DIM / DELTA_PARTS, NV = (DIM + 31) / 32 * 32, M = (DIM + 31) / 32;
   __shared__ __align__(16) float st[2][5][DIM];     // r, k, w, a u, u of the token at hand and of the next
-  const int e = blockIdx.x, h = blockIdx.y, j = threadIdx.x, lane = j & 31;
-  const bool on = j < DIM;
-  const int col = h * DIM + (on ? j : 0);
+  const int e = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+  // the thread's column, and which 16-byte pieces of a per-channel vector are its own: pieces part, part + 4, ...
+  // (the four threads of a column then read 64 bytes side by side: no two of them meet in a bank)
+  const int j = tid / DELTA_PARTS, part = tid % DELTA_PARTS;
+  const int col = h * DIM + j;
+  // the first NV threads (whole warps) also make the per-channel vectors, thread c the channel c
+  const bool maker = tid < NV, made = tid < DIM;
+  const int mcol = h * DIM + (made ? tid : 0);
   const int t0 = entry_start[e], t1 = entry_start[e + 1];
   float* slot = state + ((size_t)entry_slot[e] * n_head + h) * (size_t)DIM * DIM;
-  const float w0j = w0[col], abj = a_bias[col];
+  const float w0c = w0[mcol], abc = a_bias[mcol];
   pdl_wait();
   if (t0 >= t1) return;
-  float S[DIM];
+  float S[KPT];       // S[4 m + c] is key channel 4 (part + 4 m) + c of column j
 #pragma unroll
-  for (int i = 0; i < DIM; ++i) S[i] = on ? slot[i * DIM + j] : 0.0f;
+  for (int i = 0; i < KPT; ++i) S[i] = slot[(4 * (part + DELTA_PARTS * (i / 4)) + i % 4) * DIM + j];
 
   DeltaInputs<DIM> in;
   auto load = [&](int t) {
     const float* p = proj + (size_t)t * ld;
-    in.r = p[r_off + col]; in.k = p[k_off + col]; in.a = p[a_off + col]; in.v = p[v_off + col];
-    in.w = wl[(size_t)t * ld_w + col];
+    in.v = p[v_off + col];
+    if (maker) {
+      in.r = p[r_off + mcol]; in.k = p[k_off + mcol]; in.a = p[a_off + mcol];
+      in.w = wl[(size_t)t * ld_w + mcol];
+      if (unit != nullptr) {         // w, a u and u were made for all rows ahead of this kernel
+        in.u = unit[(size_t)t * n_head * DIM + mcol];
+      } else {
 #pragma unroll
-    for (int m = 0; m < M; ++m) {
-      const int i = lane + 32 * m;
-      in.ks[m] = i < DIM ? p[k_off + h * DIM + i] : 0.0f;
+        for (int m = 0; m < M; ++m) {
+          const int i = lane + 32 * m;
+          in.ks[m] = i < DIM ? p[k_off + h * DIM + i] : 0.0f;
+        }
+      }
     }
   };
-  auto finish = [&](int buf) {       // every warp sums the head's k^2 on its own: no barrier
+  auto finish = [&](int buf) {       // every making warp sums the head's k^2 on its own: no barrier
+    if (!maker) return;
+    if (unit != nullptr) {
+      if (made) {
+        st[buf][0][tid] = in.r; st[buf][1][tid] = in.k; st[buf][2][tid] = in.w; st[buf][3][tid] = in.a;
+        st[buf][4][tid] = in.u;
+      }
+      return;
+    }
     float ks = 0.0f;
 #pragma unroll
     for (int m = 0; m < M; ++m) ks += in.ks[m] * in.ks[m];
     ks = warp_sum(ks);
-    if (on) {
+    if (made) {
       const float u = in.k / sqrtf(ks + 1e-6f);
-      st[buf][0][j] = in.r;
-      st[buf][1][j] = in.k;
-      st[buf][2][j] = expf(-0.6065306597126334f * sigmoid_f(in.w + w0j));
-      st[buf][3][j] = sigmoid_f(in.a + abj) * u;
-      st[buf][4][j] = u;
+      st[buf][0][tid] = in.r;
+      st[buf][1][tid] = in.k;
+      st[buf][2][tid] = expf(-0.6065306597126334f * sigmoid_f(in.w + w0c));
+      st[buf][3][tid] = sigmoid_f(in.a + abc) * u;
+      st[buf][4][tid] = u;
     }
   };
   load(t0);
@@ -172,28 +224,34 @@ delta_rule_reg_kernel(const float* proj, int ld, int r_off, int k_off, int v_off
   for (int t = t0; t < t1; ++t) {
     const bool more = t + 1 < t1;
     if (more) load(t + 1);           // asked for now, used after this token's arithmetic
-    const float4* r4 = reinterpret_cast<const float4*>(st[cur][0]);
-    const float4* k4 = reinterpret_cast<const float4*>(st[cur][1]);
-    const float4* w4 = reinterpret_cast<const float4*>(st[cur][2]);
-    const float4* a4 = reinterpret_cast<const float4*>(st[cur][3]);
-    const float4* u4 = reinterpret_cast<const float4*>(st[cur][4]);
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    const float4* r4 = reinterpret_cast<const float4*>(st[cur][0]) + part;
+    const float4* k4 = reinterpret_cast<const float4*>(st[cur][1]) + part;
+    const float4* w4 = reinterpret_cast<const float4*>(st[cur][2]) + part;
+    const float4* a4 = reinterpret_cast<const float4*>(st[cur][3]) + part;
+    const float4* u4 = reinterpret_cast<const float4*>(st[cur][4]) + part;
+    float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-    for (int i = 0; i < DIM / 4; ++i) {
-      const float4 u = u4[i];
-      s0 += u.x * S[4 * i]; s1 += u.y * S[4 * i + 1]; s2 += u.z * S[4 * i + 2]; s3 += u.w * S[4 * i + 3];
+    for (int i = 0; i < KPT / 4; ++i) {
+      const float4 u = u4[DELTA_PARTS * i];
+      s0 += u.x * S[4 * i] + u.z * S[4 * i + 2];
+      s1 += u.y * S[4 * i + 1] + u.w * S[4 * i + 3];
     }
-    const float sa = (s0 + s1) + (s2 + s3);
-    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+    float sa = s0 + s1;              // u^T S over this thread's channels; the column's four threads are neighbours
+    sa += __shfl_xor_sync(0xffffffffu, sa, 1);
+    sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+    float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-    for (int i = 0; i < DIM / 4; ++i) {
-      const float4 w = w4[i], a = a4[i], k = k4[i], r = r4[i];
+    for (int i = 0; i < KPT / 4; ++i) {
+      const float4 w = w4[DELTA_PARTS * i], a = a4[DELTA_PARTS * i], k = k4[DELTA_PARTS * i], r = r4[DELTA_PARTS * i];
       S[4 * i] = w.x * S[4 * i] - a.x * sa + k.x * vc;             o0 += S[4 * i] * r.x;
       S[4 * i + 1] = w.y * S[4 * i + 1] - a.y * sa + k.y * vc;     o1 += S[4 * i + 1] * r.y;
-      S[4 * i + 2] = w.z * S[4 * i + 2] - a.z * sa + k.z * vc;     o2 += S[4 * i + 2] * r.z;
-      S[4 * i + 3] = w.w * S[4 * i + 3] - a.w * sa + k.w * vc;     o3 += S[4 * i + 3] * r.w;
+      S[4 * i + 2] = w.z * S[4 * i + 2] - a.z * sa + k.z * vc;     o0 += S[4 * i + 2] * r.z;
+      S[4 * i + 3] = w.w * S[4 * i + 3] - a.w * sa + k.w * vc;     o1 += S[4 * i + 3] * r.w;
     }
-    if (on) wl[(size_t)t * ld_w + col] = (o0 + o1) + (o2 + o3);    // the raw output where the decay logit was
+    float o = o0 + o1;
+    o += __shfl_xor_sync(0xffffffffu, o, 1);
+    o += __shfl_xor_sync(0xffffffffu, o, 2);
+    if (part == 0) wl[(size_t)t * ld_w + col] = o;                   // the raw output where the decay logit was
     if (more) {
       finish(cur ^ 1);
       vc = in.v;
@@ -201,12 +259,11 @@ delta_rule_reg_kernel(const float* proj, int ld, int r_off, int k_off, int v_off
     __syncthreads();
     cur ^= 1;
   }
-  if (on) {
 #pragma unroll
-    for (int i = 0; i < DIM; ++i) slot[i * DIM + j] = S[i];
-  }
+  for (int i = 0; i < KPT; ++i) slot[(4 * (part + DELTA_PARTS * (i / 4)) + i % 4) * DIM + j] = S[i];
   if (finish_inside)
-    delta_finish_rows<T, DIM>(proj, ld, g_off, wl, ld_w, norm_w, h, eps, out, ldo, t0 + (j >> 5), t1, NT / 32, lane);
+    delta_finish_rows<T, DIM>(proj, ld, g_off, wl, ld_w, norm_w, h, eps, out, ldo, t0 + (tid >> 5), t1,
+                              DIM * DELTA_PARTS / 32, lane);
 }
 
 template <typename T, int DIM>
@@ -222,14 +279,18 @@ delta_finish_kernel(const float* proj, int ld, int g_off, const float* raw, int 
 }
 
 template <typename T, int DIM>
-static int launch_delta_reg(const float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off, float* wl,
+static int launch_delta_reg(float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off, float* wl,
                             int ld_w, const float* w0, const float* a_bias, const float* norm_w, float* state,
                             const int* entry_start, const int* entry_slot, int n_entries, int n_rows, int n_head,
-                            float eps, T* out, int ldo, cudaStream_t stream) {
-  const int inside = n_rows == n_entries;     // single tokens: the norm of a row costs less than a launch
-  launch_pdl(delta_rule_reg_kernel<T, DIM>, dim3(n_entries, n_head), dim3((DIM + 31) / 32 * 32), 0, stream, proj, ld,
+                            float eps, T* out, int ldo, float* unit, cudaStream_t stream) {
+  // single tokens: a row's gates and its norm cost less inside the kernel than a launch each
+  const int inside = n_rows == n_entries || unit == nullptr;
+  if (!inside)
+    launch_pdl(delta_prepare_kernel, dim3((n_rows * n_head + 7) / 8), dim3(256), 0, stream, proj, ld, k_off, a_off, wl,
+               ld_w, w0, a_bias, unit, n_head, DIM, n_rows);
+  launch_pdl(delta_rule_reg_kernel<T, DIM>, dim3(n_entries, n_head), dim3(DIM * DELTA_PARTS), 0, stream, proj, ld,
              r_off, k_off, v_off, g_off, a_off, wl, ld_w, w0, a_bias, norm_w, state, entry_start, entry_slot, n_head,
-             eps, out, ldo, inside);
+             eps, out, ldo, inside, inside ? (const float*)nullptr : (const float*)unit);
   if (!inside)
     launch_pdl(delta_finish_kernel<T, DIM>, dim3((n_rows * n_head + 7) / 8), dim3(256), 0, stream, proj, ld, g_off,
                (const float*)wl, ld_w, norm_w, n_head, eps, out, ldo, n_rows);
@@ -237,14 +298,14 @@ static int launch_delta_reg(const float* proj, int ld, int r_off, int k_off, int
 }
 
 template <typename T>
-static int pick_delta_reg(int dim, const float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off,
+static int pick_delta_reg(int dim, float* proj, int ld, int r_off, int k_off, int v_off, int g_off, int a_off,
                           float* wl, int ld_w, const float* w0, const float* a_bias, const float* norm_w, float* state,
                           const int* entry_start, const int* entry_slot, int n_entries, int n_rows, int n_head,
-                          float eps, T* out, int ldo, cudaStream_t stream) {
+                          float eps, T* out, int ldo, float* unit, cudaStream_t stream) {
 #define NIB_DELTA(D)                                                                                                \
   case D:                                                                                                           \
     return launch_delta_reg<T, D>(proj, ld, r_off, k_off, v_off, g_off, a_off, wl, ld_w, w0, a_bias, norm_w, state, \
-                                  entry_start, entry_slot, n_entries, n_rows, n_head, eps, out, ldo, stream)
+                                  entry_start, entry_slot, n_entries, n_rows, n_head, eps, out, ldo, unit, stream)
   switch (dim) {
     NIB_DELTA(16); NIB_DELTA(32); NIB_DELTA(48); NIB_DELTA(64); NIB_DELTA(80); NIB_DELTA(96); NIB_DELTA(112);
     NIB_DELTA(128);
@@ -259,24 +320,26 @@ using namespace nib;
 
 // proj: float [T, ld] holding r, k, v, gate logits and removal logits at the given column offsets (n_head *
 // dim columns each); wl: float [T, ld_w] decay logits before their bias w0.  state: float [slots, n_head,
-// dim, dim].  out: [T, n_head * dim] in `dtype`.  n_rows: the rows of all entries together.  wl is scratch
-// afterwards (the kernel for head sizes in steps of 16 leaves its raw outputs there).
-extern "C" int nib_delta_rule(int dtype, const float* proj, int ld, int r_off, int k_off, int v_off, int g_off,
+// dim, dim].  out: [T, n_head * dim] in `dtype`.  n_rows: the rows of all entries together.  wl and the
+// removal logits of proj are scratch afterwards (the kernel for head sizes in steps of 16 leaves raw outputs
+// and, for steps with prompt portions, the rows' gates there); unit: float [n_rows, n_head * dim] of scratch
+// for the unit keys (may be null: the gates are then made token by token inside the recurrence).
+extern "C" int nib_delta_rule(int dtype, float* proj, int ld, int r_off, int k_off, int v_off, int g_off,
                               int a_off, float* wl, int ld_w, const float* w0, const float* a_bias,
                               const float* norm_w, float* state, const int* entry_start, const int* entry_slot,
                               int n_entries, int n_rows, int n_head, int dim, float eps, void* out, int ldo,
-                              cudaStream_t stream) {
+                              float* unit, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if (dim <= 0 || dim > 224 || n_head <= 0) return NIB_ERR_UNSUPPORTED_SIZE;
   if (dim % 16 == 0 && dim <= 128) {
     if (dtype == DT_F32)
       return pick_delta_reg<float>(dim, proj, ld, r_off, k_off, v_off, g_off, a_off, wl, ld_w, w0, a_bias, norm_w,
                                    state, entry_start, entry_slot, n_entries, n_rows, n_head, eps, (float*)out, ldo,
-                                   stream);
+                                   unit, stream);
     if (dtype == DT_BF16)
       return pick_delta_reg<bf16>(dim, proj, ld, r_off, k_off, v_off, g_off, a_off, wl, ld_w, w0, a_bias, norm_w,
                                   state, entry_start, entry_slot, n_entries, n_rows, n_head, eps, (bf16*)out, ldo,
-                                  stream);
+                                  unit, stream);
     return NIB_ERR_BAD_ARGUMENT;
   }
   const size_t smem = ((size_t)dim * dim + 5 * (size_t)dim) * sizeof(float);

@@ -154,12 +154,18 @@ latent_attention_kernel(const float* q, const T* cache, T* out, int ldo, const i
       key_page[threadIdx.x] = page;
     }
     __syncthreads();
-    for (int w = threadIdx.x; w < LA_TILE * D; w += blockDim.x) {
-      const int jj = w / D, d = w % D;
+    // every warp brings in its share of the tile's keys, a lane an element: rows of the cache as they lie
+#pragma unroll
+    for (int i = 0; i < LA_TILE / LA_WARPS; ++i) {
+      const int jj = warp * (LA_TILE / LA_WARPS) + i;
       const int page = key_page[jj];
-      float v = 0.0f;
-      if (page >= 0) v = to_float(cache[((size_t)page * page_size + (j0 + jj) % page_size) * (size_t)D + d]);
-      ktile[jj * Dp + d] = v;
+      float* dst = ktile + jj * Dp;
+      if (page >= 0) {
+        const T* srck = cache + ((size_t)page * page_size + (j0 + jj) % page_size) * (size_t)D;
+        for (int d = lane; d < D; d += 32) dst[d] = to_float(srck[d]);
+      } else {
+        for (int d = lane; d < D; d += 32) dst[d] = 0.0f;
+      }
     }
     __syncthreads();
     if (live) {

@@ -82,7 +82,8 @@ moe_route_kernel(const T* h, int ldh, const T* __restrict__ wr, int C, int n_exp
   }
 }
 
-constexpr int MOE_PER_WARP = 8;   // outputs a warp makes one after the other
+constexpr int MOE_PER_WARP = 2;   // outputs a warp makes one after the other (few: a step of few rows is bound by the
+                                  // latency of each weight row's loads, so it wants many warps at once)
 
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)

@@ -88,7 +88,7 @@ _SIGNATURES = {
                          _c_int, _c_int, _c_ptr],
     "nib_delta_rule": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
                        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int,
-                       _c_ptr],
+                       _c_ptr, _c_ptr],
     "nib_moe_route": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "nib_moe_up": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_down": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
@@ -1052,15 +1052,20 @@ def linear_heads(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torc
 # ------------------------------------------------------------------------------ delta rule
 def delta_rule(proj: torch.Tensor, offsets, wl: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor,
                norm_w: torch.Tensor, state: torch.Tensor, ctx, n_head: int, dim: int, eps: float,
-               out: torch.Tensor) -> None:
+               out: torch.Tensor, unit: Optional[torch.Tensor] = None) -> None:
     """The generalised delta rule over the step's entries (csrc/delta_rule.cu).  ``proj`` float32 [T, *] holds
     r, k, v, gate and removal logits at the column ``offsets`` (five), ``wl`` float32 the decay logits; ``state``
-    float32 [slots, n_head, dim, dim] is read and written at the entries' slots.  ``wl`` is scratch afterwards.
+    float32 [slots, n_head, dim, dim] is read and written at the entries' slots.  ``wl`` and the removal logits of
+    ``proj`` are scratch afterwards; ``unit`` (float32 [rows, n_head * dim], optional) is scratch for the rows' unit
+    keys: with it a step that carries prompt portions makes all rows' gates in one pass before the recurrence.
     ``ctx.n_rows`` counts the rows of the entries only where rows of no request follow them."""
     _f32(proj, "delta_rule: proj"); _f32(state, "delta_rule: state")
     if wl.dtype != torch.float32 or wl.stride(1) != 1 or out.stride(1) != 1 or tuple(state.shape[1:]) != (n_head, dim, dim):
         raise KernelError("delta_rule: wl float32, state [slots, heads, dim, dim]")
     r_off, k_off, v_off, g_off, a_off = (int(o) for o in offsets)
+    if unit is not None and (unit.dtype != torch.float32 or not unit.is_contiguous() or unit.shape[1] != n_head * dim
+                             or unit.shape[0] < ctx.n_rows):
+        raise KernelError("delta_rule: unit must be contiguous float32 [rows, heads * dim]")
     if tracing():
         T = ctx.n_rows
         _note("other", "delta_rule", (T, n_head * dim, dim), 8.0 * T * n_head * dim * dim,
@@ -1068,7 +1073,7 @@ def delta_rule(proj: torch.Tensor, offsets, wl: torch.Tensor, w0: torch.Tensor, 
     _check(library().nib_delta_rule(_dt(out), _ptr(proj), proj.stride(0), r_off, k_off, v_off, g_off, a_off, _ptr(wl),
                                     wl.stride(0), _ptr(w0), _ptr(a_bias), _ptr(norm_w), _ptr(state),
                                     _ptr(ctx.entry_start), _ptr(ctx.entry_slot), ctx.n_entries, ctx.n_rows, n_head,
-                                    dim, float(eps), _ptr(out), out.stride(0), _stream()), "delta_rule")
+                                    dim, float(eps), _ptr(out), out.stride(0), _ptr(unit), _stream()), "delta_rule")
 
 
 # ------------------------------------------------------------------------------ routed experts

@@ -60,6 +60,7 @@ class GeneralDeltaRule(Mixer):
         workspace.reserve("delta.lora", n * self.decay_rank, self.dtype)
         workspace.reserve("delta.decay", n * self.inner, torch.float32)
         workspace.reserve("delta.out", n * self.inner, self.dtype)
+        workspace.reserve("delta.unit", n * self.inner, torch.float32)
 
     def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: Optional[KVCacheView],
                 state: Optional[torch.Tensor], writes_cache: bool = True) -> None:
@@ -75,7 +76,8 @@ class GeneralDeltaRule(Mixer):
         ops.trace_scope(ctx.layer, "decay_up")
         ops.linear(lora, p["w2_weight"], None, wl, T)
         o = ws.get("delta.out", (n, N), self.dtype)
+        unit = ws.get("delta.unit", (n, N), torch.float32)
         ops.delta_rule(proj, (0, N, 2 * N, 3 * N, 4 * N), wl, p["w0"], p["a_bias"], p["out_norm"], state, ctx,
-                       self.n_head, self.head_dim, self.eps, o)
+                       self.n_head, self.head_dim, self.eps, o, unit)
         ops.trace_scope(ctx.layer, "delta_proj")
         ops.linear(o, p["out_weight"], None, x, T, residual=True)

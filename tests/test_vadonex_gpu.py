@@ -187,7 +187,7 @@ def test_delta_rule_kernel_carries_its_state_in_the_slot(dim):
             out.append(o.reshape(N) * nw.double() * torch.sigmoid(g[t].reshape(N)))
         return torch.stack(out), S
 
-    def run(cuts):
+    def run(cuts, with_unit=True):
         """every entry's rows in portions: one launch per round of portions"""
         state = state0.clone()
         out = torch.zeros(T + 3, N, device=DEV)
@@ -208,8 +208,9 @@ def test_delta_rule_kernel_carries_its_state_in_the_slot(dim):
                                   entry_start=torch.tensor(starts, dtype=torch.int32, device=DEV),
                                   entry_slot=torch.tensor(sl, dtype=torch.int32, device=DEV))
             o = torch.zeros(len(rows), N, device=DEV)
+            unit = torch.zeros(len(rows), N, device=DEV) if with_unit else None
             ops.delta_rule(proj[idx].contiguous(), (0, N, 2 * N, 3 * N, 4 * N), wl[idx].contiguous(), w0, ab, nw, state,
-                           ctx, H, dim, eps, o)
+                           ctx, H, dim, eps, o, unit)
             out[idx] = o
         return out, state
 
@@ -219,10 +220,10 @@ def test_delta_rule_kernel_carries_its_state_in_the_slot(dim):
         o, S = plain(list(range(at, at + n)), state0[s])
         want[at:at + n], want_state[s] = o, S
         at += n
-    for cuts in (1000, 1, 2, 5):
-        got, state = run(cuts)
-        assert float((got[:T] - want).abs().max()) < 2e-4, cuts
-        assert float((state - want_state).abs().max()) < 2e-4, cuts      # untouched slots stay as they were
+    for cuts, with_unit in ((1000, True), (1000, False), (1, True), (2, True), (5, True), (5, False)):
+        got, state = run(cuts, with_unit)
+        assert float((got[:T] - want).abs().max()) < 2e-4, (cuts, with_unit)
+        assert float((state - want_state).abs().max()) < 2e-4, (cuts, with_unit)   # untouched slots stay as they were
 
 
 def _latent_case(dtype, kv_rank, rot, page, window, positions, hot, n_splits=None):
