@@ -180,6 +180,9 @@ int nib_moe_up(int dtype, const void* h, int ldh, const void* w_up, const int* i
                int F, int top, int act, cudaStream_t stream);
 int nib_moe_down(int dtype, const void* inner, const void* w_down, const int* ids, const float* weights, float* x,
                  int T, int C, int F, int top, cudaStream_t stream);
+// inner [T, n_expert * F] in place: expert e's part of row t times the row's weight for e (0 where not chosen).
+int nib_moe_scale(int dtype, void* inner, const int* ids, const float* weights, int T, int n_expert, int F, int top,
+                  cudaStream_t stream);
 // Expert-major forms for steps of many rows: phase 0 = up (out [T * top, N] in dtype), phase 1 = down into
 // out float [T * top, N] (weighted), phase 2 = x[t] += the sum of row t's parts (src = the parts).
 int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src, const void* w, const int* ids,

@@ -15,6 +15,14 @@
 // (each warp scans the step's choices for its own share of them; a lane per output, the row broadcast from
 // shared memory).  The second product leaves each (row, choice)'s weighted result in a buffer of its own and
 // moe_combine adds a row's choices into the stream in the order of the choices: no atomics, a fixed order.
+//
+// Where the experts are few for what a row chooses, a step of many rows does better still with ALL experts as two
+// products of the engine's own (tensor cores): act(h . [W_up of all experts]^T) in one product, every expert's
+// part of a row scaled by the row's weight for it or by 0 (moe_scale), then every expert's second matrix on its
+// part, one product an expert, all adding into the stream.  n_expert / top times the arithmetic, on another
+// class of unit.  (The second matrices side by side as ONE matrix [C, n_expert * F] would make that one product
+// too; it was built and cost the row-by-row kernel of decode steps half its speed, its weight rows then lying
+// n_expert * F apart, so the stacked layout stayed.)
 #include <algorithm>
 
 #include "api.h"
@@ -204,6 +212,23 @@ moe_grouped_kernel(const T* src, int ld_src, const T* __restrict__ w, const int*
   if (nf > 0) run();
 }
 
+// inner [T, n_expert * F]: expert e's part of row t is multiplied by the row's weight for e, by 0 where the row
+// did not choose e (so that one product over all experts' second matrices adds up the chosen ones only).
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_scale_kernel(T* inner, const int* ids, const float* weights, int n_expert, int F, int top, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t t = i / ((size_t)n_expert * F);
+  const int e = (int)((i / F) % n_expert);
+  float s = 0.0f;
+  for (int k = 0; k < top; ++k)
+    if (ids[t * top + k] == e) s = weights[t * top + k];
+  inner[i] = from_float<T>(s == 0.0f ? 0.0f : s * to_float(inner[i]));
+}
+
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* parts, float* x, int C, int top, size_t n) {
   pdl_trigger();
   pdl_wait();
@@ -334,5 +359,19 @@ extern "C" int nib_moe_down(int dtype, const void* inner, const void* w_down, co
   } else {
     return NIB_ERR_BAD_ARGUMENT;
   }
+  NIB_LAUNCH_CHECK();
+}
+
+extern "C" int nib_moe_scale(int dtype, void* inner, const int* ids, const float* weights, int T, int n_expert, int F,
+                             int top, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const size_t n = (size_t)T * n_expert * F;
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (dtype == DT_F32)
+    launch_pdl(moe_scale_kernel<float>, grid, dim3(256), 0, stream, (float*)inner, ids, weights, n_expert, F, top, n);
+  else if (dtype == DT_BF16)
+    launch_pdl(moe_scale_kernel<bf16>, grid, dim3(256), 0, stream, (bf16*)inner, ids, weights, n_expert, F, top, n);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();
 }

@@ -92,6 +92,7 @@ _SIGNATURES = {
     "nib_moe_route": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "nib_moe_up": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_down": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "nib_moe_scale": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_grouped": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                         _c_int, _c_int, _c_int, _c_ptr],
 }
@@ -1119,17 +1120,50 @@ def moe_down(inner: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weigh
                                   top, _stream()), "moe_down")
 
 
-#: rows per expert (on average) from which the routed feed-forward runs expert by expert, each tile of an
-#: expert's matrix staged once, instead of row by row
+#: rows per expert (on average) from which the routed feed-forward leaves the row-by-row kernels
 MOE_GROUPED_MIN_ROWS_PER_EXPERT = 8
+#: the most experts per chosen expert for which a step of many rows runs ALL experts as two products on the tensor
+#: cores (n_expert / top times the arithmetic of the chosen ones) rather than expert by expert on the CUDA cores
+MOE_DENSE_MAX_RATIO = 8
 MOE_GROUPED = True
+MOE_DENSE = True
+
+
+def moe_dense_pays(T: int, top: int, n_expert: int) -> bool:
+    return MOE_DENSE and T * top >= MOE_GROUPED_MIN_ROWS_PER_EXPERT * n_expert and n_expert <= MOE_DENSE_MAX_RATIO * top
+
+
+def moe_scale(inner_all: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, T: int, n_expert: int, F: int,
+              top: int) -> None:
+    """inner_all [T, n_expert * F] in place: expert e's part of row t times weights[t, k] where ids[t, k] == e,
+    times 0 where the row did not choose e."""
+    if not inner_all.is_contiguous() or inner_all.shape[1] != n_expert * F:
+        raise KernelError("moe_scale: inner_all contiguous [T, experts * F]")
+    if tracing():
+        _note("other", "experts_mask", (T, n_expert * F, 0), T * n_expert * F, 2.0 * T * n_expert * F * inner_all.element_size())
+    _check(library().nib_moe_scale(_dt(inner_all), _ptr(inner_all), _ptr(ids), _ptr(weights), T, n_expert, F, top,
+                                   _stream()), "moe_scale")
 
 
 def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
                 inner: torch.Tensor, x: torch.Tensor, T: int, top: int, act: int, workspace) -> None:
-    """x[t] += sum_k weights[t, k] * w_down[ids[t, k]] . act(w_up[ids[t, k]] . h[t]): row by row for steps of few
-    rows, expert by expert (weights staged in shared memory, a fixed order of additions) for steps of many."""
+    """x[t] += sum_k weights[t, k] * W_down[ids[t, k]] . act(W_up[ids[t, k]] . h[t]) with w_up [experts, F, C] and
+    w_down [experts, C, F].  Steps of few rows: row by row.  Steps of many rows: all experts through the engine's
+    own products with the unchosen ones scaled to zero in between (``moe_dense_pays``: the first matrices as one
+    product, the second ones a product an expert, all adding into the stream), else expert by expert (weights
+    staged in shared memory, a fixed order of additions)."""
     E, F, C = w_up.shape
+    if tuple(w_down.shape) != (E, C, F):
+        raise KernelError("moe_experts: w_down must be [experts, C, F]")
+    if moe_dense_pays(T, top, E):
+        inner_all = workspace.get("moe.inner_all", (x.shape[0], E * F), h.dtype)
+        trace_scope(_rec.layer if _rec is not None else -1, "experts_up")
+        linear(h, w_up.view(E * F, C), None, inner_all, T, act=act)
+        moe_scale(inner_all, ids, weights, T, E, F, top)
+        trace_scope(_rec.layer if _rec is not None else -1, "experts_down")
+        for e in range(E):
+            linear(inner_all[:, e * F:(e + 1) * F], w_down[e], None, x, T, residual=True)
+        return
     es = h.element_size()
     fits = all(32 * (K + 2) * es + 4 * K * 16 <= 200 * 1024 for K in (C, F))   # a tile of 32 outputs, four rows a warp
     grouped = MOE_GROUPED and T * top >= MOE_GROUPED_MIN_ROWS_PER_EXPERT * E and fits

@@ -47,8 +47,9 @@ class RoutedExperts(FeedForward):
     def prepare(self, dtype, device) -> None:
         super().prepare(dtype, device)
         p, E = self.params, self.n_expert
-        # the experts' matrices stacked, so that a kernel finds expert e at a fixed stride; the parameters
-        # by name become views of the stacks (no second copy stays behind)
+        # the experts' matrices stacked, [E, F, C] and [E, C, F]: a kernel finds expert e at a fixed stride, and
+        # the first matrices of all experts are one matrix [E * F, C]; the parameters by name become views of
+        # the stacks (no second copy stays behind)
         self.w_up = torch.stack([p[f"expert{e}_up"] for e in range(E)], 0).contiguous()
         self.w_down = torch.stack([p[f"expert{e}_down"] for e in range(E)], 0).contiguous()
         for e in range(E):
@@ -60,6 +61,8 @@ class RoutedExperts(FeedForward):
         workspace.reserve("moe.weights", n * self.top, torch.float32)
         workspace.reserve("moe.inner", n * self.top * self.inner, self.dtype)
         workspace.reserve("moe.parts", n * self.top * self.width, torch.float32)
+        if self.n_expert <= ops.MOE_DENSE_MAX_RATIO * self.top:
+            workspace.reserve("moe.inner_all", n * self.n_expert * self.inner, self.dtype)
         if self.shared_inner:
             workspace.reserve("moe.shared", n * self.shared_inner, self.dtype)
 

@@ -132,7 +132,7 @@ def test_routing_kernels_against_torch(E, top, C, F, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("E,top,C,F", [(4, 2, 72, 50), (3, 1, 130, 33), (8, 3, 256, 96)])
-def test_experts_row_by_row_and_expert_by_expert_agree(E, top, C, F, dtype):
+def test_experts_row_by_row_expert_by_expert_and_all_at_once_agree(E, top, C, F, dtype):
     from nanoinfer_b200.kernels import ops
     from nanoinfer_b200.parts.base import Workspace
 
@@ -142,23 +142,26 @@ def test_experts_row_by_row_and_expert_by_expert_agree(E, top, C, F, dtype):
     up, down = (torch.randn(E, F, C, device=DEV) * 0.2).to(dt), (torch.randn(E, C, F, device=DEV) * 0.2).to(dt)
     ids = torch.stack([torch.randperm(E)[:top] for _ in range(T)]).to(torch.int32).to(DEV)
     wts = torch.rand(T, top, device=DEV)
-    x0 = torch.randn(T, C, device=DEV)
+    x0 = torch.randn(T + 10, C, device=DEV)
     got = {}
-    for grouped in (False, True):
-        ops.MOE_GROUPED = grouped
+    for form, (dense, grouped) in {"row by row": (False, False), "expert by expert": (False, True),
+                                   "all experts at once": (True, True)}.items():
+        ops.MOE_DENSE, ops.MOE_GROUPED = dense, grouped
         try:
             x, inner = x0.clone(), torch.zeros(T * top, F, device=DEV, dtype=dt)
             ops.moe_experts(h, up, down, ids, wts, inner, x, T, top, ops.ACT_GELU_ERF, Workspace(torch.device(DEV)))
-            got[grouped] = (x, inner)
+            got[form] = x
         finally:
-            ops.MOE_GROUPED = True
+            ops.MOE_DENSE = ops.MOE_GROUPED = True
     pre = torch.einsum("tc,tkfc->tkf", h.double(), up.double()[ids.long()])
-    mid = (0.5 * pre * (1 + torch.erf(pre / math.sqrt(2)))).to(dt).double()
-    want = x0.double() + torch.einsum("tk,tkf,tkcf->tc", wts.double(), mid, down.double()[ids.long()])
-    tol = 1e-4 if dtype == "float32" else 0.05
-    for grouped, (x, inner) in got.items():
-        assert float((x - want).abs().max()) < tol, grouped
-    assert float((got[True][0] - got[False][0]).abs().max()) < tol / 10 + 1e-5
+    mid = 0.5 * pre * (1 + torch.erf(pre / math.sqrt(2)))
+    want = x0[:T].double() + torch.einsum("tk,tkf,tkcf->tc", wts.double(), mid, down.double()[ids.long()])
+    # (in bfloat16 the inner activations, in one form times their weight, are rounded to 8 bits: the bound goes
+    # with the size of the sums)
+    tol = 1e-4 if dtype == "float32" else 0.01 * float(want.abs().max())
+    for form, x in got.items():
+        assert float((x[:T] - want).abs().max()) < tol, form
+        assert torch.equal(x[T:], x0[T:]), form
 
 
 @pytest.mark.parametrize("dim", [16, 40, 48, 64, 128])
