@@ -19,9 +19,10 @@ extern "C" {
 #endif
 
 // A negative token -(s + 1) stands for feedback[s]: the token that the step before sampled for
-// slot s and left on the device (feedback may be null when no token is negative).
+// slot s and left on the device (feedback may be null when no token is negative).  out = table[token] * scale
+// (+ pos_table[position]).
 int nib_embed(int dtype, const int* tokens, const int* positions, const void* table,
-              const void* pos_table, const int* feedback, float* out, int T, int C, cudaStream_t stream);
+              const void* pos_table, const int* feedback, float* out, int T, int C, float scale, cudaStream_t stream);
 
 int nib_layernorm(int out_dtype, const float* x, const int* rows, const float* gamma,
                   const float* beta, void* out, int n_rows, int C, float eps, cudaStream_t stream);
@@ -81,11 +82,12 @@ int nib_linear_skinny(int out_dtype, const void* a, int lda, const void* w, int 
                       int split, int* status, cudaStream_t stream);
 
 // Causal attention of T query rows over the paged cache (general SIMT kernel).  rows: the
-// step's rows to process (nullptr: rows 0..T-1).
+// step's rows to process (nullptr: rows 0..T-1).  `sink` (here and in the attention kernels below): 1 adds one
+// term exp(0) to the softmax's denominator, a key of score 0 that has no value.
 int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, void* out, int ldo,
                        const int* block_table, int max_blocks, const int* rows, const int* row_entry,
                        const int* positions, int T, int n_head, int n_kv_head, int head_dim,
-                       int page_size, int n_pages, float scale, int window, int* status,
+                       int page_size, int n_pages, float scale, int window, int sink, int* status,
                        cudaStream_t stream);
 
 // tcgen05 attention for prompt portions (bfloat16, head size 64, page size a multiple of 16): tiles of
@@ -94,7 +96,7 @@ int nib_attention_prefill_tc_supported(int head_dim, int page_size);
 int nib_attention_prefill_tc(const void* q, int ldq, int T, const void* cache, void* out, int ldo,
                              const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                              const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head, int head_dim,
-                             int page_size, int n_pages, float scale, int window, int* status, cudaStream_t stream);
+                             int page_size, int n_pages, float scale, int window, int sink, int* status, cudaStream_t stream);
 
 // Split-KV attention for single decoded tokens (float32 or bfloat16, head sizes up to 128 in steps
 // of 8, pages of a multiple of 16 positions) and its scratch need.
@@ -102,7 +104,7 @@ long long nib_attention_decode_scratch(int n_rows, int n_head, int head_dim, int
 int nib_attention_decode(int dtype, const void* q, int ldq, const void* cache, float* scratch, void* out,
                          int ldo, const int* block_table, int max_blocks, const int* rows,
                          const int* row_entry, const int* positions, int n_rows, int n_head, int n_kv_head,
-                         int head_dim, int page_size, int n_pages, float scale, int window, int chunk,
+                         int head_dim, int page_size, int n_pages, float scale, int window, int sink, int chunk,
                          int n_splits, int* counters, int* status, cudaStream_t stream);
 
 // Tiled tensor-core attention for prompt portions (bfloat16, head sizes 16..128 in steps of 16).
@@ -110,7 +112,7 @@ int nib_attention_prefill_supported(int head_dim);
 int nib_attention_prefill(const void* q, int ldq, const void* cache, void* out, int ldo,
                           const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                           const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
-                          int head_dim, int page_size, int n_pages, float scale, int window, int* status,
+                          int head_dim, int page_size, int n_pages, float scale, int window, int sink, int* status,
                           cudaStream_t stream);
 
 // Loading: src holds [rows, cols] values as a checkpoint stores them (src_dtype 0: 32-bit floats, 1:
@@ -149,6 +151,26 @@ int nib_post_norm(int out_dtype, float* x, const float* w, float eps, float* lev
 int nib_unary(int in_dtype, int out_dtype, const void* in, int ld_in, void* out, int ld_out, int n_rows,
               int n_cols, int kind, const float* prm, cudaStream_t stream);
 
+// x += y / sqrt(mean(y^2) + eps) * w_out; y = 0; with w_next: xn = cast(x / sqrt(mean(x^2) + eps) * w_next).
+int nib_add_norm(int out_dtype, float* x, float* y, const float* w_out, const float* w_next, float eps, void* xn,
+                 int n_rows, int C, cudaStream_t stream);
+// out[t, f] = act(pre[t, 2f]) * pre[t, 2f + 1], times sigmoid(pre[t, row_gate]) where row_gate >= 0.
+int nib_glu(int in_dtype, int out_dtype, const void* pre, int ld, void* out, int ldo, int n_rows, int F, int act,
+            int row_gate, cudaStream_t stream);
+
+// ---- rotary positions with the cast and the cache append (rope.cu)
+int nib_rope_append(int dtype, const float* proj, int ld, int q_off, int k_off, int v_off, int n_head, int n_kv_head,
+                    int dim, int vdim, int hd, int rot_dims, const double* freqs, const int* positions,
+                    const int* row_entry, void* q_out, int ldq, void* cache, const int* block_table, int max_blocks,
+                    int page_size, int n_pages, int T, int* status, cudaStream_t stream);
+
+// ---- the matrix memory of xLSTM (mlstm.cu)
+long long nib_mlstm_state_floats(int dim, int vdim);
+int nib_mlstm(int dtype, const float* proj, int ld, int q_off, int k_off, int v_off, int g_off, int i_off, int f_off,
+              const float* bias_i, const float* bias_f, float cap, const float* norm_w, float* state,
+              const int* entry_start, const int* entry_slot, int n_entries, int n_rows, int n_head, int dim, int vdim,
+              float eps, float* gates, float* num, int ld_num, float* den, void* out, int ldo, cudaStream_t stream);
+
 // ---- attention through a shared low-rank latent (latent_attention.cu)
 int nib_latent_prep(int dtype, const float* proj, int ld, int q_rank, int kv_rank, int rot_dim, int rot_dims,
                     const double* freqs, const float* wq, const float* wkv, float eps, void* cq, int ld_cq,
@@ -174,16 +196,22 @@ int nib_delta_rule(int dtype, float* proj, int ld, int r_off, int k_off, int v_o
                    int dim, float eps, void* out, int ldo, float* unit, cudaStream_t stream);
 
 // ---- a routed feed-forward (moe.cu)
+// score 0: softmax over all experts; 1: the sigmoids of the chosen experts' logits.
 int nib_moe_route(int dtype, const void* h, int ldh, const void* w_router, int T, int C, int n_expert, int top,
-                  int renorm, int* ids, float* weights, cudaStream_t stream);
+                  int renorm, int score, int* ids, float* weights, cudaStream_t stream);
+// gated: w_up [experts, 2F, C], rows 2f and 2f + 1 the gate and the value of output f; inner = act(s g) * (s u) with
+// s = in_weights[t * top + k] (null: 1).
 int nib_moe_up(int dtype, const void* h, int ldh, const void* w_up, const int* ids, void* inner, int T, int C,
-               int F, int top, int act, cudaStream_t stream);
+               int F, int top, int act, int gated, const float* in_weights, cudaStream_t stream);
+int nib_moe_gate_scale(int pre_dtype, int dtype, const void* pre, void* inner, const int* ids, const float* weights,
+                       int T, int n_expert, int F, int top, int act, int on_input, cudaStream_t stream);
 int nib_moe_down(int dtype, const void* inner, const void* w_down, const int* ids, const float* weights, float* x,
                  int T, int C, int F, int top, cudaStream_t stream);
 // inner [T, n_expert * F] in place: expert e's part of row t times the row's weight for e (0 where not chosen).
 int nib_moe_scale(int dtype, void* inner, const int* ids, const float* weights, int T, int n_expert, int F, int top,
                   cudaStream_t stream);
-// Expert-major forms for steps of many rows: phase 0 = up (out [T * top, N] in dtype), phase 1 = down into
+// Expert-major forms for steps of many rows: phase 0 = up (out [T * top, N] in dtype; phase 3: gated, N = 2F
+// interleaved rows, out [T * top, F], weights scaling the inputs), phase 1 = down into
 // out float [T * top, N] (weighted), phase 2 = x[t] += the sum of row t's parts (src = the parts).
 int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src, const void* w, const int* ids,
                     const float* weights, void* out, float* x, int T, int top, int n_expert, int N, int K, int act,

@@ -70,7 +70,7 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
                         const int* __restrict__ row_entry, const int* __restrict__ positions, int n_head,
                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale, int window,
-                        int chunk, int n_splits, int* counters, int* status,
+                        int sink, int chunk, int n_splits, int* counters, int* status,
                         int cluster_merge) {
   constexpr int VN = Piece<T>::N;
   constexpr int BATCH = LPR / 2 < 4 ? LPR / 2 : 4;   // keys per lane group and batch
@@ -225,11 +225,14 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
   for (int w = 0; w < ALL_GROUPS; ++w) M = fmaxf(M, gm[w]);
   float L = 0.0f;
   for (int w = 0; w < ALL_GROUPS; ++w) L += (gm[w] == -INFINITY) ? 0.0f : gl[w] * pow2<T>(gm[w] - M);
+  // a sink (one more term in the denominator: a key of score 0 without a value) counts once, where the row's
+  // weights are divided
+  const float L1 = (sink && n_splits == 1) ? L + pow2<T>(-M) : L;
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
     for (int w = 0; w < ALL_GROUPS; ++w) acc += (gm[w] == -INFINITY) ? 0.0f : go[w * head_dim + d] * pow2<T>(gm[w] - M);
     if (n_splits == 1)
-      out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / L);
+      out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / L1);
     else if (cluster_merge)
       store_to_rank(xo + split * head_dim + d, 0, acc);
     else
@@ -275,6 +278,7 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
     const float ls = part_ml[2 * (base + sp) + 1];
     if (ls > 0.0f) Lx += ls * pow2<T>(part_ml[2 * (base + sp)] - Mx);
   }
+  if (sink) Lx += pow2<T>(-Mx);
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
     for (int sp = 0; sp < n_splits; ++sp) {
@@ -289,7 +293,7 @@ template <typename T>
 static int launch_decode(const void* q, int ldq, const void* cache, float* part_o, float* part_ml, void* out,
                          int ldo, const int* block_table, int max_blocks, const int* rows, const int* row_entry,
                          const int* positions, int n_rows, int n_head, int n_kv_head, int head_dim,
-                         int page_size, int n_pages, float scale, int window, int chunk, int n_splits,
+                         int page_size, int n_pages, float scale, int window, int sink, int chunk, int n_splits,
                          int* counters, int* status, cudaStream_t stream) {
   dim3 grid(n_splits, n_head, n_rows);
   const int n_pieces = head_dim / Piece<T>::N;
@@ -300,8 +304,8 @@ static int launch_decode(const void* q, int ldq, const void* cache, float* part_
   launch_pdl_cluster(attention_decode_kernel<T, LPR>, dim3(grid), dim3(DEC_WARPS * 32),                            \
              (size_t)(DEC_WARPS * (32 / LPR) * (head_dim + 2) + n_splits * (head_dim + 2)) * sizeof(float), stream, \
              cluster, (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks,   \
-             rows, row_entry, positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk,    \
-             n_splits, counters, status, cluster > 1 ? 1 : 0)
+             rows, row_entry, positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, sink,     \
+             chunk, n_splits, counters, status, cluster > 1 ? 1 : 0)
   if (n_pieces <= 2) NIB_DECODE_LAUNCH(2);
   else if (n_pieces <= 4) NIB_DECODE_LAUNCH(4);
   else if (n_pieces <= 8) NIB_DECODE_LAUNCH(8);
@@ -329,7 +333,7 @@ extern "C" int nib_attention_decode(int dtype, const void* q, int ldq, const voi
                                     void* out, int ldo, const int* block_table, int max_blocks, const int* rows,
                                     const int* row_entry, const int* positions, int n_rows, int n_head,
                                     int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
-                                    int window, int chunk, int n_splits, int* counters, int* status,
+                                    int window, int sink, int chunk, int n_splits, int* counters, int* status,
                                     cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (head_dim <= 0 || head_dim > DEC_MAX_HD || (head_dim & 7)) return NIB_ERR_UNSUPPORTED_SIZE;
@@ -342,11 +346,11 @@ extern "C" int nib_attention_decode(int dtype, const void* q, int ldq, const voi
   if (dtype == DT_F32)
     return launch_decode<float>(q, ldq, cache, part_o, part_ml, out, ldo, block_table, max_blocks, rows, row_entry,
                                 positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
-                                chunk, n_splits, counters, status, stream);
+                                sink, chunk, n_splits, counters, status, stream);
   if (dtype == DT_BF16)
     return launch_decode<bf16>(q, ldq, cache, part_o, part_ml, out, ldo, block_table, max_blocks, rows, row_entry,
                                positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
-                               chunk, n_splits, counters, status, stream);
+                               sink, chunk, n_splits, counters, status, stream);
   return NIB_ERR_BAD_ARGUMENT;
 }
 
@@ -407,5 +411,5 @@ extern "C" int nib_attention_decode_static(int dtype, const void* q, int ldq, co
   if (e != cudaSuccess) return (int)e;
   return nib_attention_decode(dtype, q, ldq, cache, scratch, out, ldo, block_table, max_blocks, rows, row_entry,
                               positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
-                              chunk, n_splits, counters, status, stream);
+                              0, chunk, n_splits, counters, status, stream);
 }

@@ -73,7 +73,7 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
                             float* part_ml, bf16* out, int ldo, const int* __restrict__ block_table,
                             int max_blocks, const int* __restrict__ rows, const int* __restrict__ row_entry,
                             const int* __restrict__ positions, int n_head, int n_kv_head, int page_size,
-                            int n_pages, float scale, int window, int chunk, int n_splits,
+                            int n_pages, float scale, int window, int sink, int chunk, int n_splits,
                             int* counters, int* status, int cluster_merge) {
   constexpr int HALVES = HD / 32;                    // a 16-byte piece per lane covers 32 of a row's values
   constexpr bool RING = STAGES > 0;
@@ -313,12 +313,14 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
     float L = 0.0f;
 #pragma unroll
     for (int w = 0; w < DM_WARPS; ++w) L += (wm[w] == -INFINITY) ? 0.0f : wl[w] * dm_pow2(wm[w] - M);
+    // (a sink, one more term exp(0) in the denominator, counts once: where the row's weights are divided)
+    const float L1 = (sink && n_splits == 1 && M != -INFINITY) ? L + dm_pow2(-M) : L;
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
       float o = 0.0f;
 #pragma unroll
       for (int w = 0; w < DM_WARPS; ++w) o += (wm[w] == -INFINITY) ? 0.0f : wo[w][d] * dm_pow2(wm[w] - M);
       if (n_splits == 1)
-        out[(size_t)t * ldo + h * HD + d] = __float2bfloat16_rn(L > 0.0f ? o / L : 0.0f);
+        out[(size_t)t * ldo + h * HD + d] = __float2bfloat16_rn(L1 > 0.0f ? o / L1 : 0.0f);
       else if (cluster_merge)
         store_to_rank(&xo[split][d], 0, o);
       else
@@ -367,6 +369,7 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
     const float ls = ml[2 * sp + 1];
     if (ls > 0.0f) Lx += ls * dm_pow2(ml[2 * sp] - Mx);
   }
+  if (sink && Mx != -INFINITY) Lx += dm_pow2(-Mx);
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float o = 0.0f;
     for (int sp = 0; sp < n_splits; ++sp) {
@@ -432,7 +435,7 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
                                         int ldo, const int* block_table, int max_blocks, const int* rows,
                                         const int* row_entry, const int* positions, int n_rows, int n_head,
                                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
-                                        int window, int chunk, int n_splits, int* counters, int* status,
+                                        int window, int sink, int chunk, int n_splits, int* counters, int* status,
                                         int cluster, int ring, cudaStream_t stream) {
   if (ring != 0 && ring != 2 && ring != 3 && ring != 4) return NIB_ERR_BAD_ARGUMENT;
   if (n_rows <= 0) return 0;
@@ -472,7 +475,7 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
     e = launch_pdl_cluster(attention_decode_mma_kernel<HD, RING>, grid, block, RING > 0 ? ring_bytes : 0, stream, \
                            cluster ? n_splits : 1, (const bf16*)q, ldq, (const bf16*)cache, part_o, part_ml,     \
                            (bf16*)out, ldo, block_table, max_blocks, rows, row_entry, positions, n_head,         \
-                           n_kv_head, page_size, n_pages, scale, window, chunk, n_splits, counters, status,      \
+                           n_kv_head, page_size, n_pages, scale, window, sink, chunk, n_splits, counters, status, \
                            cluster ? 1 : 0);                                                                     \
   } while (0)
 #define NIB_DM_LAUNCH(HD)                   \

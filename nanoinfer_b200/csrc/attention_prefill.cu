@@ -60,7 +60,7 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
                          int ldo, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ tiles, const int* __restrict__ entry_start,
                          const int* __restrict__ entry_pos0, int n_head, int n_kv_head, int page_size, int n_pages,
-                         float scale, int window, int* __restrict__ status) {
+                         float scale, int window, int sink, int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   constexpr int LD = HD + 8;               // padded row: ldmatrix reads without bank conflicts
@@ -251,6 +251,10 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
     const float a0 = pow2(m0 - ms0), a1 = pow2(m1 - ms1), b0 = pow2(other.x - ms0), b1 = pow2(other.y - ms1);
     l0 = l0 * a0 + other.z * b0;
     l1 = l1 * a1 + other.w * b1;
+    if (sink) {   // one more term in the denominator: a key of score 0 that has no value
+      if (mn0 != -INFINITY) l0 += pow2(-mn0);
+      if (mn1 != -INFINITY) l1 += pow2(-mn1);
+    }
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
       const float4 t = *reinterpret_cast<const float4*>(mine + 4 * i);
@@ -277,7 +281,7 @@ template <int HD>
 static int launch_prefill(const void* q, int ldq, const void* cache, void* out, int ldo, const int* block_table,
                           int max_blocks, const int* tiles, int n_tiles, const int* entry_start,
                           const int* entry_pos0, int n_head, int n_kv_head, int page_size, int n_pages, float scale,
-                          int window, int* status, cudaStream_t stream) {
+                          int window, int sink, int* status, cudaStream_t stream) {
   const size_t smem = (size_t)(PF_BM + 4 * PF_BN) * (HD + 8) * sizeof(bf16);
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
@@ -289,7 +293,7 @@ static int launch_prefill(const void* q, int ldq, const void* cache, void* out, 
   dim3 grid(n_head, n_tiles);
   launch_pdl(attention_prefill_kernel<HD>, dim3(grid), dim3(PF_THREADS), smem, stream, 
       (const bf16*)q, ldq, (const bf16*)cache, (bf16*)out, ldo, block_table, max_blocks, tiles, entry_start,
-      entry_pos0, n_head, n_kv_head, page_size, n_pages, scale, window, status);
+      entry_pos0, n_head, n_kv_head, page_size, n_pages, scale, window, sink, status);
   NIB_LAUNCH_CHECK();
 }
 
@@ -308,7 +312,7 @@ extern "C" int nib_attention_prefill(const void* q, int ldq, const void* cache, 
                                      const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                                      const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
                                      int head_dim, int page_size, int n_pages, float scale, int window,
-                                     int* status, cudaStream_t stream) {
+                                     int sink, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (!nib_attention_prefill_supported(head_dim)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f)) return NIB_ERR_BAD_ARGUMENT;
@@ -317,7 +321,7 @@ extern "C" int nib_attention_prefill(const void* q, int ldq, const void* cache, 
 #define NIB_PF_CASE(D)                                                                                         \
   case D:                                                                                                      \
     return launch_prefill<D>(q, ldq, cache, out, ldo, block_table, max_blocks, tiles, n_tiles, entry_start,    \
-                             entry_pos0, n_head, n_kv_head, page_size, n_pages, scale, window, status, stream);
+                             entry_pos0, n_head, n_kv_head, page_size, n_pages, scale, window, sink, status, stream);
   switch (head_dim) {
     NIB_PF_CASE(16) NIB_PF_CASE(32) NIB_PF_CASE(48) NIB_PF_CASE(64) NIB_PF_CASE(80) NIB_PF_CASE(96)
     NIB_PF_CASE(112) NIB_PF_CASE(128)

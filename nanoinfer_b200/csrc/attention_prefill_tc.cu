@@ -40,6 +40,7 @@ struct AtParams {
   int n_head, n_kv_head, page_size, n_pages;
   float scale;
   int window;
+  int sink;      // 1: the softmax's denominator has one more term, exp(0) (a key of score 0 without a value)
   bf16* out;
   int ldo;
   int* status;
@@ -332,6 +333,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok) ok = warp_mbar_wait(&o_full[(n_it - 1) % AT_NBUF], ((n_it - 1) / AT_NBUF) & 1, abort_flag, lane);
     if (ok) {
       tc_fence_after();
+      if (prm.sink && m != -INFINITY) l += at_pow2(-m);
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       bf16* dst = prm.out + (size_t)(row0 + r) * prm.ldo + h * AT_HD;
 #pragma unroll 1
@@ -373,7 +375,7 @@ extern "C" int nib_attention_prefill_tc(const void* q, int ldq, int T, const voi
                                         const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                                         const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
                                         int head_dim, int page_size, int n_pages, float scale, int window,
-                                        int* status, cudaStream_t stream) {
+                                        int sink, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (!nib_attention_prefill_tc_supported(head_dim, page_size)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f) || T <= 0) return NIB_ERR_BAD_ARGUMENT;
@@ -389,7 +391,7 @@ extern "C" int nib_attention_prefill_tc(const void* q, int ldq, int T, const voi
   prm.block_table = block_table; prm.max_blocks = max_blocks; prm.tiles = tiles;
   prm.entry_start = entry_start; prm.entry_pos0 = entry_pos0;
   prm.n_head = n_head; prm.n_kv_head = n_kv_head; prm.page_size = page_size; prm.n_pages = n_pages;
-  prm.scale = scale; prm.window = window; prm.out = (bf16*)out; prm.ldo = ldo; prm.status = status;
+  prm.scale = scale; prm.window = window; prm.sink = sink; prm.out = (bf16*)out; prm.ldo = ldo; prm.status = status;
   // 128 keys a tile, one block an SM: measured a little faster than 64 keys a tile and two blocks
   constexpr int BN = 128;
   static bool attr_set = false;

@@ -6,7 +6,8 @@
 // for the keys j <= pos, softmax with the maximum subtracted, o = sum_j p_j v_j.  The
 // softmax runs online over blocks of 32 keys (the split/merge rule of
 // crates/metal/src/shaders/batch.metal:349-424), all in 32-bit.  A row's result depends on
-// its own keys only, never on what else the batch holds.
+// its own keys only, never on what else the batch holds.  With `sink` the softmax's denominator has one
+// more term, exp(0): a key of score 0 that has no value, so that a row may attend to nothing.
 #include "api.h"
 #include "common.cuh"
 
@@ -21,7 +22,7 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
                       T* out, int ldo, const int* __restrict__ block_table,
                       int max_blocks, const int* __restrict__ rows, const int* __restrict__ row_entry,
                       const int* __restrict__ positions, int n_head, int n_kv_head, int head_dim,
-                      int page_size, int n_pages, float scale, int window, int* __restrict__ status) {
+                      int page_size, int n_pages, float scale, int window, int sink, int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float smem[];
@@ -87,6 +88,8 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
     __syncwarp();
     m = m_new;
   }
+  // a sink: one more term in the denominator, a key of score 0 that has no value
+  if (sink) l += expf(-m);
   const float inv = 1.0f / l;
 #pragma unroll
   for (int i = 0; i < ATT_MAX_ND; ++i) {
@@ -103,7 +106,7 @@ extern "C" int nib_attention_simt(int dtype, const void* q, int ldq, const void*
                                   int ldo, const int* block_table, int max_blocks, const int* rows,
                                   const int* row_entry, const int* positions, int T, int n_head,
                                   int n_kv_head, int head_dim, int page_size, int n_pages,
-                                  float scale, int window, int* status, cudaStream_t stream) {
+                                  float scale, int window, int sink, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (head_dim <= 0 || head_dim > 32 * ATT_MAX_ND || (head_dim & 1)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
@@ -113,11 +116,11 @@ extern "C" int nib_attention_simt(int dtype, const void* q, int ldq, const void*
   if (dtype == DT_F32)
     launch_pdl(attention_simt_kernel<float>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const float*)q, ldq, (const float*)cache, (float*)out, ldo, block_table, max_blocks, rows, row_entry,
-        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, status);
+        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, sink, status);
   else if (dtype == DT_BF16)
     launch_pdl(attention_simt_kernel<bf16>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const bf16*)q, ldq, (const bf16*)cache, (bf16*)out, ldo, block_table, max_blocks, rows, row_entry,
-        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, status);
+        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, sink, status);
   else
     return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();

@@ -15,7 +15,8 @@ using bf16 = __nv_bfloat16;
 enum : int { DT_F32 = 0, DT_BF16 = 1 };
 
 // activation codes of the linear epilogues
-enum : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2 };
+// (ACT_SILU is taken by the element-wise and expert kernels only, not by the products' epilogues)
+enum : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2, ACT_RELU_SQ = 3, ACT_SILU = 4 };
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
@@ -33,9 +34,16 @@ __device__ __forceinline__ float gelu_tanh(float u) {
 __device__ __forceinline__ float gelu_erf(float u) {
   return 0.5f * u * (1.0f + erff(u * 0.7071067811865476f));
 }
+// the square of relu: max(u, 0)^2
+__device__ __forceinline__ float relu_sq(float u) {
+  const float r = fmaxf(u, 0.0f);
+  return r * r;
+}
 __device__ __forceinline__ float apply_act(float u, int act) {
   if (act == ACT_GELU_TANH) return gelu_tanh(u);
   if (act == ACT_GELU_ERF) return gelu_erf(u);
+  if (act == ACT_RELU_SQ) return relu_sq(u);
+  if (act == ACT_SILU) return u / (1.0f + expf(-u));
   return u;
 }
 

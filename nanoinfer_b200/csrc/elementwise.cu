@@ -16,7 +16,7 @@ namespace nib {
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                              const T* __restrict__ table, const T* __restrict__ pos_table,
-                             const int* feedback, float* out, int C) {
+                             const int* feedback, float* out, int C, float scale) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -26,9 +26,9 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
   float* o = out + (size_t)t * C;
   if (pos_table != nullptr) {
     const T* pe = pos_table + (size_t)positions[t] * C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) o[c] = to_float(te[c]) + to_float(pe[c]);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) o[c] = to_float(te[c]) * scale + to_float(pe[c]);
   } else {
-    for (int c = threadIdx.x; c < C; c += blockDim.x) o[c] = to_float(te[c]);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) o[c] = to_float(te[c]) * scale;
   }
 }
 
@@ -182,15 +182,15 @@ using namespace nib;
 
 extern "C" int nib_embed(int dtype, const int* tokens, const int* positions, const void* table,
                          const void* pos_table, const int* feedback, float* out, int T, int C,
-                         cudaStream_t stream) {
+                         float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   const int threads = C >= 256 ? 256 : 128;
   if (dtype == DT_F32)
     launch_pdl(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, positions, (const float*)table,
-                                                   (const float*)pos_table, feedback, out, C);
+                                                   (const float*)pos_table, feedback, out, C, scale);
   else if (dtype == DT_BF16)
     launch_pdl(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, tokens, positions, (const bf16*)table,
-                                                  (const bf16*)pos_table, feedback, out, C);
+                                                  (const bf16*)pos_table, feedback, out, C, scale);
   else
     return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();

@@ -391,6 +391,8 @@ linear_skinny_kernel(const SkinnyParams prm) {
         x = 0.5f * x * (1.0f + th);
       } else if (prm.act == ACT_GELU_ERF) {
         x = gelu_erf(x);
+      } else if (prm.act == ACT_RELU_SQ) {
+        x = relu_sq(x);
       }
       if (prm.kv_cache != nullptr && n >= prm.kv_q_dim) {
         const int kv_dim = prm.kv_heads * prm.kv_head_dim;

@@ -89,6 +89,7 @@ __device__ __forceinline__ float epilogue_act(float u) {
     return 0.5f * u * (1.0f + t);
   }
   if (ACT == ACT_GELU_ERF) return gelu_erf(u);
+  if (ACT == ACT_RELU_SQ) return relu_sq(u);
   return u;
 }
 // ------------------------------------------------------------------ the kernel
@@ -711,6 +712,9 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(linear_tc_kernel<ACT_GELU_ERF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                225 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(linear_tc_kernel<ACT_RELU_SQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               225 * 1024);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
@@ -720,6 +724,8 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
     launch_pdl(linear_tc_kernel<ACT_GELU_TANH>, grid, dim3(TC_THREADS), smem, stream, map_p, map_q, map_o, prm);
   else if (act == ACT_GELU_ERF)
     launch_pdl(linear_tc_kernel<ACT_GELU_ERF>, grid, dim3(TC_THREADS), smem, stream, map_p, map_q, map_o, prm);
+  else if (act == ACT_RELU_SQ)
+    launch_pdl(linear_tc_kernel<ACT_RELU_SQ>, grid, dim3(TC_THREADS), smem, stream, map_p, map_q, map_o, prm);
   else if (act == ACT_NONE)
     launch_pdl(linear_tc_kernel<ACT_NONE>, grid, dim3(TC_THREADS), smem, stream, map_p, map_q, map_o, prm);
   else

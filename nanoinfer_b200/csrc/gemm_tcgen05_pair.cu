@@ -92,6 +92,7 @@ __device__ __forceinline__ float pair_act(float u) {
     return 0.5f * u * (1.0f + t);
   }
   if (ACT == ACT_GELU_ERF) return gelu_erf(u);
+  if (ACT == ACT_RELU_SQ) return relu_sq(u);
   return u;
 }
 
@@ -439,6 +440,7 @@ extern "C" int nib_linear_tc_pair(int out_dtype, const void* a, int lda, const v
   if (grid.y > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
   if (act == ACT_GELU_TANH) return launch_pair<ACT_GELU_TANH>(map_a, map_w, map_o, prm, grid, smem, stream);
   if (act == ACT_GELU_ERF) return launch_pair<ACT_GELU_ERF>(map_a, map_w, map_o, prm, grid, smem, stream);
+  if (act == ACT_RELU_SQ) return launch_pair<ACT_RELU_SQ>(map_a, map_w, map_o, prm, grid, smem, stream);
   if (act == ACT_NONE) return launch_pair<ACT_NONE>(map_a, map_w, map_o, prm, grid, smem, stream);
   return NIB_ERR_BAD_ARGUMENT;
 }

@@ -1,0 +1,261 @@
+// The matrix memory of xLSTM (mLSTM): a recurrent mixer whose state per head is a matrix S [key channel, value
+// channel], a vector n [key channel] and a running maximum mx of the log gates, kept so that the exponentials
+// of the gates never overflow.  Per token and head, with log input gate gi and log forget gate gf (both <= cap):
+//   gi  = cap * tanh((z_i + b_i) / cap),   gf = logsigmoid(cap * tanh((z_f + b_f) / cap))
+//   mx' = max(gf + mx, gi)                                  (mx starts at 0)
+//   S'  = exp(gf + mx - mx') S + exp(gi - mx') k v^T,       n' likewise with k alone
+//   o   = S'^T q / (max(|n' . q|, exp(-mx')) + 1e-6),       q scaled by dim^(-1/2)
+// then each head's o is divided by its root mean square, multiplied by a weight and by sigmoid(gate).
+//
+// Three kernels:
+//   mlstm_gates  : a block per (batch entry, head).  What does not depend on S: the gates of all the entry's rows,
+//                  the running maximum (a serial pass of one thread over 256 rows at a time), and from them the two
+//                  factors exp(gf + mx - mx'), exp(gi - mx') and the floor exp(-mx') of every row.  mx goes back to
+//                  the request's slot.
+//   mlstm_scan   : a block per (entry, head, 64 value channels) walks the entry's rows in order.  A column of S
+//                  belongs to one value channel and the columns do not see one another; n is one more column whose
+//                  value is 1 (the first block of a head carries it).  A column lives in the registers of four
+//                  neighbouring threads, which take the 16-byte pieces r, r + 4, r + 8, ... of q and k (the four
+//                  read 64 bytes side by side: no bank conflicts; S^T q is a sum over four lanes, two shuffles).  The
+//                  next row's q, k, v and factors pass through a double buffer in shared memory: one barrier a row.
+//                  It leaves the numerators S'^T q and the denominators.
+//   mlstm_finish : a warp per (row, head): the division, the head's root mean square, weight and gate.
+// The projections come in as 32-bit floats; everything here is 32-bit.  State per slot and head:
+// [value channels + 1][dim rounded up to 16] floats (the last column is n), then mx and three unused floats.
+#include "api.h"
+#include "common.cuh"
+
+namespace nib {
+
+constexpr int ML_VC = 64;                 // value channels a block
+constexpr int ML_THREADS = 4 * (ML_VC + 8);   // 288: the columns, the column of n, and lanes that only carry loads
+constexpr int ML_GATE_ROWS = 256;
+
+__device__ __forceinline__ float ml_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float ml_logsigmoid(float v) { return fminf(v, 0.0f) - log1pf(expf(-fabsf(v))); }
+
+__global__ void __launch_bounds__(ML_GATE_ROWS)
+mlstm_gates_kernel(const float* proj, int ld, int i_off, int f_off, const float* __restrict__ bias_i,
+                   const float* __restrict__ bias_f, float cap, float* state, long long slot_stride,
+                   long long head_stride, const int* __restrict__ entry_start, const int* __restrict__ entry_slot,
+                   int n_head, float* gates) {
+  pdl_trigger();
+  __shared__ float gi[ML_GATE_ROWS], gf[ML_GATE_ROWS], gm[ML_GATE_ROWS + 1];
+  const int e = blockIdx.x, h = blockIdx.y, i = threadIdx.x;
+  const int t0 = entry_start[e], t1 = entry_start[e + 1];
+  float* mx_at = state + (size_t)entry_slot[e] * slot_stride + (size_t)(h + 1) * head_stride - 4;
+  const float bi = bias_i[h], bf = bias_f[h], inv_cap = 1.0f / cap;
+  pdl_wait();
+  if (i == 0) gm[0] = *mx_at;
+  for (int base = t0; base < t1; base += ML_GATE_ROWS) {
+    const int n = min(ML_GATE_ROWS, t1 - base);
+    if (i < n) {
+      const float* p = proj + (size_t)(base + i) * ld;
+      gi[i] = cap * tanhf((p[i_off + h] + bi) * inv_cap);
+      gf[i] = ml_logsigmoid(cap * tanhf((p[f_off + h] + bf) * inv_cap));
+    }
+    __syncthreads();
+    if (i == 0) {
+      float m = gm[0];
+#pragma unroll 8
+      for (int j = 0; j < n; ++j) {
+        m = fmaxf(gf[j] + m, gi[j]);
+        gm[j + 1] = m;
+      }
+    }
+    __syncthreads();
+    if (i < n) {
+      const float m = gm[i + 1];
+      float* g = gates + ((size_t)(base + i) * n_head + h) * 4;
+      g[0] = expf(gf[i] + gm[i] - m);
+      g[1] = expf(gi[i] - m);
+      g[2] = expf(-m);
+    }
+    const float last = gm[n];
+    __syncthreads();
+    if (i == 0) gm[0] = last;
+  }
+  if (i == 0) *mx_at = gm[0];
+}
+
+// NP: 16-byte pieces of q (and of k) a thread holds: dim rounded up to 16, over 16.
+template <int NP>
+__global__ void __launch_bounds__(ML_THREADS)
+mlstm_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, const float* gates, float* state,
+                  long long slot_stride, long long head_stride, const int* __restrict__ entry_start,
+                  const int* __restrict__ entry_slot, int n_head, int dim, int vdim, float q_scale, float* num,
+                  int ld_num, float* den) {
+  pdl_trigger();
+  constexpr int DP = 16 * NP;                       // dim rounded up
+  constexpr int STAGE = 2 * DP + ML_VC + 4;         // q | k | v of the block's channels | the row's three factors
+  constexpr int NL = (STAGE + ML_THREADS - 1) / ML_THREADS;
+  __shared__ __align__(16) float stage[2][STAGE];
+  const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * ML_VC, tid = threadIdx.x;
+  const int jc = tid >> 2, r = tid & 3;
+  const int t0 = entry_start[e], t1 = entry_start[e + 1];
+  // this thread's column: a value channel of the block, or (first block of the head) the column of n
+  const bool is_n = jc == ML_VC && blockIdx.z == 0;
+  const int col = is_n ? vdim : c0 + jc;
+  const bool live = is_n || (jc < ML_VC && col < vdim);
+  float* column = state + (size_t)entry_slot[e] * slot_stride + (size_t)h * head_stride + (size_t)col * DP;
+  // what this thread brings in of a row: element idx of the stage
+  auto fetch = [&](int t, float* regs) {
+    const float* p = proj + (size_t)t * ld;
+#pragma unroll
+    for (int l = 0; l < NL; ++l) {
+      const int idx = tid + l * ML_THREADS;
+      float v = 0.0f;
+      if (idx < DP) {
+        if (idx < dim) v = p[q_off + h * dim + idx] * q_scale;
+      } else if (idx < 2 * DP) {
+        if (idx - DP < dim) v = p[k_off + h * dim + idx - DP];
+      } else if (idx < 2 * DP + ML_VC) {
+        const int ch = c0 + idx - 2 * DP;
+        if (ch < vdim) v = p[v_off + h * vdim + ch];
+      } else if (idx < 2 * DP + ML_VC + 3) {
+        v = gates[((size_t)t * n_head + h) * 4 + idx - 2 * DP - ML_VC];
+      }
+      regs[l] = v;
+    }
+  };
+  auto put = [&](int buf, const float* regs) {
+#pragma unroll
+    for (int l = 0; l < NL; ++l) {
+      const int idx = tid + l * ML_THREADS;
+      if (idx < STAGE) stage[buf][idx] = regs[l];
+    }
+  };
+  pdl_wait();
+  if (t0 >= t1) return;
+  float4 S[NP];
+#pragma unroll
+  for (int p = 0; p < NP; ++p)
+    S[p] = live ? reinterpret_cast<const float4*>(column)[p * 4 + r] : make_float4(0.f, 0.f, 0.f, 0.f);
+  float regs[NL];
+  fetch(t0, regs);
+  put(0, regs);
+  __syncthreads();
+  for (int t = t0; t < t1; ++t) {
+    const int buf = (t - t0) & 1;
+    if (t + 1 < t1) fetch(t + 1, regs);
+    const float* st = stage[buf];
+    const float keep = st[2 * DP + ML_VC], take = st[2 * DP + ML_VC + 1];
+    const float tv = take * (is_n ? 1.0f : st[2 * DP + (jc < ML_VC ? jc : 0)]);
+    const float4* q4 = reinterpret_cast<const float4*>(st);
+    const float4* k4 = reinterpret_cast<const float4*>(st + DP);
+    float acc = 0.0f;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const float4 q = q4[p * 4 + r], k = k4[p * 4 + r];
+      S[p].x = fmaf(keep, S[p].x, tv * k.x);
+      S[p].y = fmaf(keep, S[p].y, tv * k.y);
+      S[p].z = fmaf(keep, S[p].z, tv * k.z);
+      S[p].w = fmaf(keep, S[p].w, tv * k.w);
+      acc = fmaf(S[p].x, q.x, acc);
+      acc = fmaf(S[p].y, q.y, acc);
+      acc = fmaf(S[p].z, q.z, acc);
+      acc = fmaf(S[p].w, q.w, acc);
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (r == 0 && live) {
+      if (is_n)
+        den[(size_t)t * n_head + h] = fmaxf(fabsf(acc), st[2 * DP + ML_VC + 2]) + 1e-6f;
+      else
+        num[(size_t)t * ld_num + h * vdim + col] = acc;
+    }
+    if (t + 1 < t1) put(buf ^ 1, regs);
+    __syncthreads();
+  }
+  if (live) {
+#pragma unroll
+    for (int p = 0; p < NP; ++p) reinterpret_cast<float4*>(column)[p * 4 + r] = S[p];
+  }
+}
+
+// out[t, h, :] = (num / den) over its root mean square, times the weight, times sigmoid(gate); a warp a (row, head)
+template <typename T>
+__global__ void __launch_bounds__(256)
+mlstm_finish_kernel(const float* num, int ld_num, const float* den, const float* proj, int ld, int g_off,
+                    const float* __restrict__ norm_w, float eps, T* out, int ldo, int n_head, int vdim, int n_rows) {
+  pdl_trigger();
+  const int wi = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  pdl_wait();
+  if (wi >= n_rows * n_head) return;
+  const int t = wi / n_head, h = wi % n_head;
+  const float inv = 1.0f / den[(size_t)t * n_head + h];
+  const float* src = num + (size_t)t * ld_num + h * vdim;
+  float sq = 0.0f;
+  for (int j = lane; j < vdim; j += 32) {
+    const float o = src[j] * inv;
+    sq += o * o;
+  }
+  const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)vdim + eps);
+  for (int j = lane; j < vdim; j += 32) {
+    const int c = h * vdim + j;
+    out[(size_t)t * ldo + c] = from_float<T>(src[j] * inv * rstd * norm_w[c] * ml_sigmoid(proj[(size_t)t * ld + g_off + c]));
+  }
+}
+
+template <int NP>
+static cudaError_t launch_scan(dim3 grid, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off, int v_off,
+                               const float* gates, float* state, long long slot_stride, long long head_stride,
+                               const int* entry_start, const int* entry_slot, int n_head, int dim, int vdim,
+                               float q_scale, float* num, int ld_num, float* den) {
+  return launch_pdl(mlstm_scan_kernel<NP>, grid, dim3(ML_THREADS), 0, stream, proj, ld, q_off, k_off, v_off, gates, state,
+                    slot_stride, head_stride, entry_start, entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den);
+}
+
+}  // namespace nib
+
+using namespace nib;
+
+// Floats of state per head: nib_mlstm_state_floats(dim, vdim) (the slot holds n_head times that).
+extern "C" long long nib_mlstm_state_floats(int dim, int vdim) {
+  const long long dp = (dim + 15) / 16 * 16;
+  return (long long)(vdim + 1) * dp + 4;
+}
+
+// proj [rows, ld] float: the projections q, k (n_head x dim each), v, g (n_head x vdim each) and the two gate
+// logits (n_head each) at their column offsets.  gates [rows, n_head, 4], num [rows, ld_num >= n_head * vdim] and
+// den [rows, n_head] are scratch.  out [rows, ldo] in `dtype` receives n_head * vdim values a row.
+extern "C" int nib_mlstm(int dtype, const float* proj, int ld, int q_off, int k_off, int v_off, int g_off, int i_off,
+                         int f_off, const float* bias_i, const float* bias_f, float cap, const float* norm_w,
+                         float* state, const int* entry_start, const int* entry_slot, int n_entries, int n_rows,
+                         int n_head, int dim, int vdim, float eps, float* gates, float* num, int ld_num, float* den,
+                         void* out, int ldo, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0 || dim > 256 || vdim <= 0 || n_head <= 0 || n_head > 65535 || !(cap > 0.0f)) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (n_entries > 0) {
+    const long long head_stride = nib_mlstm_state_floats(dim, vdim), slot_stride = head_stride * n_head;
+    launch_pdl(mlstm_gates_kernel, dim3(n_entries, n_head), dim3(ML_GATE_ROWS), 0, stream, proj, ld, i_off, f_off, bias_i,
+               bias_f, cap, state, slot_stride, head_stride, entry_start, entry_slot, n_head, gates);
+    const dim3 grid(n_entries, n_head, (vdim + ML_VC - 1) / ML_VC);
+    if (grid.z > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
+    const float q_scale = 1.0f / sqrtf((float)dim);
+    cudaError_t err;
+#define NIB_ML_CASE(NP)                                                                                             \
+  case NP:                                                                                                          \
+    err = launch_scan<NP>(grid, stream, proj, ld, q_off, k_off, v_off, gates, state, slot_stride, head_stride,      \
+                          entry_start, entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den);                   \
+    break;
+    switch ((dim + 15) / 16) {
+      NIB_ML_CASE(1) NIB_ML_CASE(2) NIB_ML_CASE(3) NIB_ML_CASE(4) NIB_ML_CASE(5) NIB_ML_CASE(6) NIB_ML_CASE(7)
+      NIB_ML_CASE(8) NIB_ML_CASE(9) NIB_ML_CASE(10) NIB_ML_CASE(11) NIB_ML_CASE(12) NIB_ML_CASE(13) NIB_ML_CASE(14)
+      NIB_ML_CASE(15) NIB_ML_CASE(16)
+      default: return NIB_ERR_UNSUPPORTED_SIZE;
+    }
+#undef NIB_ML_CASE
+    if (err != cudaSuccess) return (int)err;
+  }
+  const dim3 fgrid((n_rows * n_head + 7) / 8);
+  if (dtype == DT_F32)
+    launch_pdl(mlstm_finish_kernel<float>, fgrid, dim3(256), 0, stream, num, ld_num, den, proj, ld, g_off, norm_w, eps,
+               (float*)out, ldo, n_head, vdim, n_rows);
+  else if (dtype == DT_BF16)
+    launch_pdl(mlstm_finish_kernel<bf16>, fgrid, dim3(256), 0, stream, num, ld_num, den, proj, ld, g_off, norm_w, eps,
+               (bf16*)out, ldo, n_head, vdim, n_rows);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
+  NIB_LAUNCH_CHECK();
+}

@@ -23,6 +23,13 @@
 // class of unit.  (The second matrices side by side as ONE matrix [C, n_expert * F] would make that one product
 // too; it was built and cost the row-by-row kernel of decode steps half its speed, its weight rows then lying
 // n_expert * F apart, so the stacked layout stayed.)
+//
+// Variants that a model's configuration chooses: scores that are sigmoids of the logits instead of a softmax
+// (`score` 1; the choice is then made on the logits themselves, which order the experts as their sigmoids do and do
+// not saturate); gated experts W_down (act(W_gate h) * (W_up h)) whose first two matrices lie interleaved in one
+// (row 2f the gate's, row 2f + 1 the value's: `gated`); and the chosen expert's score multiplying its INPUT instead
+// of its output (the first product is linear, so the score scales its two results before the activation, and the
+// second product then runs with a null `weights`).
 #include <algorithm>
 
 #include "api.h"
@@ -34,8 +41,8 @@ constexpr int MOE_WARPS = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
-moe_route_kernel(const T* h, int ldh, const T* __restrict__ wr, int C, int n_expert, int top, int renorm, int* ids,
-                 float* weights) {
+moe_route_kernel(const T* h, int ldh, const T* __restrict__ wr, int C, int n_expert, int top, int renorm, int score,
+                 int* ids, float* weights) {
   pdl_trigger();
   extern __shared__ float smem[];
   float* row = smem;               // [C]
@@ -53,23 +60,25 @@ moe_route_kernel(const T* h, int ldh, const T* __restrict__ wr, int C, int n_exp
     if (lane == 0) prob[e] = s;
   }
   __syncthreads();
-  float mx = -INFINITY;
-  for (int e = threadIdx.x; e < n_expert; e += blockDim.x) mx = fmaxf(mx, prob[e]);
-  mx = block_max(mx, scratch);
-  float sum = 0.0f;
-  for (int e = threadIdx.x; e < n_expert; e += blockDim.x) sum += expf(prob[e] - mx);
-  sum = block_sum(sum, scratch);
-  __syncthreads();
-  for (int e = threadIdx.x; e < n_expert; e += blockDim.x) prob[e] = expf(prob[e] - mx) / sum;
-  __syncthreads();
+  if (score == 0) {   // softmax over all experts (score 1: the logits stay, the chosen ones' sigmoids are the scores)
+    float mx = -INFINITY;
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) mx = fmaxf(mx, prob[e]);
+    mx = block_max(mx, scratch);
+    float sum = 0.0f;
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) sum += expf(prob[e] - mx);
+    sum = block_sum(sum, scratch);
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) prob[e] = expf(prob[e] - mx) / sum;
+    __syncthreads();
+  }
   if (warp == 0) {
     float total = 0.0f;
     for (int k = 0; k < top; ++k) {
-      float best = -1.0f;
+      float best = -INFINITY;
       int at = -1;
       for (int e = lane; e < n_expert; e += 32) {
         const float p = prob[e];
-        if (p > best) { best = p; at = e; }      // (a taken expert holds -2; a NaN is never larger)
+        if (p > best) { best = p; at = e; }      // (a taken expert holds -inf; a NaN is never larger)
       }
       for (int o = 16; o > 0; o >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, o);
@@ -77,10 +86,11 @@ moe_route_kernel(const T* h, int ldh, const T* __restrict__ wr, int C, int n_exp
         if (oa >= 0 && (at < 0 || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
       }
       if (at < 0) { at = k % n_expert; best = 0.0f; }   // rows that hold no numbers (rows of no request)
+      else if (score == 1) best = 1.0f / (1.0f + expf(-best));
       if (lane == 0) {
         ids[(size_t)t * top + k] = at;
         weights[(size_t)t * top + k] = best;
-        prob[at] = -2.0f;
+        prob[at] = -INFINITY;
       }
       total += best;
       __syncwarp();
@@ -96,7 +106,7 @@ constexpr int MOE_PER_WARP = 2;   // outputs a warp makes one after the other (f
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_up_kernel(const T* h, int ldh, const T* __restrict__ w_up, const int* ids, T* inner, int C, int F, int top,
-              int act) {
+              int act, int gated, const float* in_weights) {
   pdl_trigger();
   extern __shared__ float row[];   // [C]
   const int p = blockIdx.x, t = p / top, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -105,6 +115,21 @@ moe_up_kernel(const T* h, int ldh, const T* __restrict__ w_up, const int* ids, T
   for (int c = threadIdx.x; c < C; c += blockDim.x) row[c] = to_float(h[(size_t)t * ldh + c]);
   __syncthreads();
   const int f0 = (blockIdx.y * MOE_WARPS + warp) * MOE_PER_WARP;
+  if (gated) {   // rows 2f and 2f + 1 of the expert's matrix are output f's gate and value
+    const float ws = in_weights ? in_weights[p] : 1.0f;
+    for (int f = f0; f < min(F, f0 + MOE_PER_WARP); ++f) {
+      const T* w = w_up + ((size_t)e * F + f) * 2 * C;
+      float g = 0.0f, u = 0.0f;
+      for (int c = lane; c < C; c += 32) {
+        g += row[c] * to_float(w[c]);
+        u += row[c] * to_float(w[C + c]);
+      }
+      g = warp_sum(g);
+      u = warp_sum(u);
+      if (lane == 0) inner[(size_t)p * F + f] = from_float<T>(apply_act(ws * g, act) * (ws * u));
+    }
+    return;
+  }
   for (int f = f0; f < min(F, f0 + MOE_PER_WARP); ++f) {
     const T* w = w_up + ((size_t)e * F + f) * C;
     float s = 0.0f;
@@ -132,7 +157,7 @@ moe_down_kernel(const T* inner, const T* __restrict__ w_down, const int* ids, co
       const float* r = rows + k * F;
       float s = 0.0f;
       for (int f = lane; f < F; f += 32) s += r[f] * to_float(w[f]);
-      total += weights[(size_t)t * top + k] * warp_sum(s);
+      total += (weights ? weights[(size_t)t * top + k] : 1.0f) * warp_sum(s);
     }
     if (lane == 0) x[(size_t)t * C + c] += total;
   }
@@ -141,7 +166,9 @@ moe_down_kernel(const T* inner, const T* __restrict__ w_down, const int* ids, co
 constexpr int MOE_G_WARPS = 4, MOE_G_OUT = 32, MOE_G_ROWS = 4;
 
 // MODE 0: out[p, n] = act(W[e][n] . src[p / top])   (src: the rows, out: T [P, N])
-// MODE 1: out[p, n] = weights[p] * (W[e][n] . src[p])   (src: the inner activations [P, K], out: float [P, N])
+// MODE 1: out[p, n] = weights[p] * (W[e][n] . src[p])   (src: the inner activations [P, K], out: float [P, N]; null weights: 1)
+// MODE 2: out[p, n / 2] = act(s g) * (s u), g and u the products of rows n, n + 1 (n even) of W[e] with src[p / top],
+//         s = weights[p] (null: 1): gated experts, out T [P, N / 2]
 // A warp collects four (row, choice) pairs of the block's expert at a time and lays their inputs side by side
 // ([K][4] floats), so that one 16-byte read serves four multiply-adds beside one read of the lane's weight.
 template <typename T, typename TO, int MODE>
@@ -165,7 +192,7 @@ moe_grouped_kernel(const T* src, int ld_src, const T* __restrict__ w, const int*
   auto run = [&]() {                      // the products of the nf pairs in `found` with the block's tile
     const T* s[MOE_G_ROWS];
 #pragma unroll
-    for (int i = 0; i < MOE_G_ROWS; ++i) s[i] = src + (size_t)(i < nf ? (MODE == 0 ? found[i] / top : found[i]) : 0) * ld_src;
+    for (int i = 0; i < MOE_G_ROWS; ++i) s[i] = src + (size_t)(i < nf ? (MODE != 1 ? found[i] / top : found[i]) : 0) * ld_src;
     __syncwarp();
 #pragma unroll 4
     for (int k = lane; k < K; k += 32)
@@ -180,14 +207,23 @@ moe_grouped_kernel(const T* src, int ld_src, const T* __restrict__ w, const int*
       acc.x += a.x * wv; acc.y += a.y * wv; acc.z += a.z * wv; acc.w += a.w * wv;
     }
     const float v[MOE_G_ROWS] = {acc.x, acc.y, acc.z, acc.w};
-    if (n0 + lane < N) {
+    if (MODE == 2) {   // a gate and its value lie in neighbouring lanes
+#pragma unroll
+      for (int i = 0; i < MOE_G_ROWS; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
+        if (i < nf && !(lane & 1) && n0 + lane + 1 < N) {
+          const float ws = weights ? weights[found[i]] : 1.0f;
+          out[(size_t)found[i] * (N / 2) + (n0 + lane) / 2] = from_float<TO>(apply_act(ws * v[i], act) * (ws * other));
+        }
+      }
+    } else if (n0 + lane < N) {
 #pragma unroll
       for (int i = 0; i < MOE_G_ROWS; ++i) {
         if (i < nf) {
           if (MODE == 0)
             out[(size_t)found[i] * N + n0 + lane] = from_float<TO>(apply_act(v[i], act));
           else
-            out[(size_t)found[i] * N + n0 + lane] = from_float<TO>(weights[found[i]] * v[i]);
+            out[(size_t)found[i] * N + n0 + lane] = from_float<TO>((weights ? weights[found[i]] : 1.0f) * v[i]);
         }
       }
     }
@@ -227,6 +263,31 @@ moe_scale_kernel(T* inner, const int* ids, const float* weights, int n_expert, i
   for (int k = 0; k < top; ++k)
     if (ids[t * top + k] == e) s = weights[t * top + k];
   inner[i] = from_float<T>(s == 0.0f ? 0.0f : s * to_float(inner[i]));
+}
+
+// The gated form of the same: pre [T, n_expert * 2F] holds every expert's (gate, value) pairs side by side; inner
+// [T, n_expert * F] = act(s g) * (s u) with `on_input`, else s * act(g) * u; s the row's weight for the expert, and 0
+// where the row did not choose it.
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+moe_gate_scale_kernel(const TI* pre, T* inner, const int* ids, const float* weights, int n_expert, int F, int top,
+                      int act, int on_input, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t t = i / ((size_t)n_expert * F);
+  const int e = (int)((i / F) % n_expert);
+  float s = 0.0f;
+  bool chosen = false;
+  for (int k = 0; k < top; ++k)
+    if (ids[t * top + k] == e) { s = weights[t * top + k]; chosen = true; }
+  float v = 0.0f;
+  if (chosen) {
+    const float g = to_float(pre[2 * i]), u = to_float(pre[2 * i + 1]);
+    v = on_input ? apply_act(s * g, act) * (s * u) : s * apply_act(g, act) * u;
+  }
+  inner[i] = from_float<T>(v);
 }
 
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* parts, float* x, int C, int top, size_t n) {
@@ -270,7 +331,8 @@ static int launch_moe_grouped(const T* src, int ld_src, const T* w, const int* i
 
 using namespace nib;
 
-// The expert-major form of nib_moe_up (phase 0), nib_moe_down into `parts` float [T * top, C] (phase 1), and the sum of
+// The expert-major form of nib_moe_up (phase 0; phase 3: gated, N = 2F interleaved rows, out [T * top, F], `weights`
+// scaling the inputs), nib_moe_down into `parts` float [T * top, C] (phase 1), and the sum of
 // a row's parts into the stream (phase 2).  -2 where a tile of an expert's matrix does not fit shared memory.
 extern "C" int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src, const void* w, const int* ids,
                                const float* weights, void* out, float* x, int T, int top, int n_expert, int N, int K,
@@ -282,6 +344,9 @@ extern "C" int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src
     NIB_LAUNCH_CHECK();
   }
   if (dtype == DT_F32) {
+    if (phase == 3)
+      return launch_moe_grouped<float, float, 2>((const float*)src, ld_src, (const float*)w, ids, weights, (float*)out,
+                                                 T * top, top, n_expert, N, K, act, stream);
     if (phase == 0)
       return launch_moe_grouped<float, float, 0>((const float*)src, ld_src, (const float*)w, ids, weights, (float*)out,
                                                  T * top, top, n_expert, N, K, act, stream);
@@ -289,6 +354,9 @@ extern "C" int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src
                                                T * top, top, n_expert, N, K, act, stream);
   }
   if (dtype == DT_BF16) {
+    if (phase == 3)
+      return launch_moe_grouped<bf16, bf16, 2>((const bf16*)src, ld_src, (const bf16*)w, ids, weights, (bf16*)out,
+                                               T * top, top, n_expert, N, K, act, stream);
     if (phase == 0)
       return launch_moe_grouped<bf16, bf16, 0>((const bf16*)src, ld_src, (const bf16*)w, ids, weights, (bf16*)out,
                                                T * top, top, n_expert, N, K, act, stream);
@@ -299,28 +367,29 @@ extern "C" int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src
 }
 
 extern "C" int nib_moe_route(int dtype, const void* h, int ldh, const void* w_router, int T, int C, int n_expert,
-                             int top, int renorm, int* ids, float* weights, cudaStream_t stream) {
+                             int top, int renorm, int score, int* ids, float* weights, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (top <= 0 || top > n_expert || C <= 0) return NIB_ERR_BAD_ARGUMENT;
+  if (top <= 0 || top > n_expert || C <= 0 || (score != 0 && score != 1)) return NIB_ERR_BAD_ARGUMENT;
   const size_t smem = (size_t)(C + n_expert) * sizeof(float);
   if (smem > 200 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
   if (dtype == DT_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(moe_route_kernel<float>, dim3(T), dim3(MOE_WARPS * 32), smem, stream, (const float*)h, ldh,
-               (const float*)w_router, C, n_expert, top, renorm, ids, weights);
+               (const float*)w_router, C, n_expert, top, renorm, score, ids, weights);
   } else if (dtype == DT_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(moe_route_kernel<bf16>, dim3(T), dim3(MOE_WARPS * 32), smem, stream, (const bf16*)h, ldh,
-               (const bf16*)w_router, C, n_expert, top, renorm, ids, weights);
+               (const bf16*)w_router, C, n_expert, top, renorm, score, ids, weights);
   } else {
     return NIB_ERR_BAD_ARGUMENT;
   }
   NIB_LAUNCH_CHECK();
 }
 
-// inner: [T * top, F] in `dtype`; act: an activation code of the linear epilogues.
+// inner: [T * top, F] in `dtype`; act: an activation code.  gated: w_up is [experts, 2F, C] with rows 2f, 2f + 1 the
+// gate and value of output f, and in_weights (may be null) [T * top] scale the inputs.
 extern "C" int nib_moe_up(int dtype, const void* h, int ldh, const void* w_up, const int* ids, void* inner, int T,
-                          int C, int F, int top, int act, cudaStream_t stream) {
+                          int C, int F, int top, int act, int gated, const float* in_weights, cudaStream_t stream) {
   if (T <= 0) return 0;
   const size_t smem = (size_t)C * sizeof(float);
   if (smem > 200 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
@@ -329,11 +398,11 @@ extern "C" int nib_moe_up(int dtype, const void* h, int ldh, const void* w_up, c
   if (dtype == DT_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(moe_up_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, stream, (const float*)h, ldh,
-               (const float*)w_up, ids, (float*)inner, C, F, top, act);
+               (const float*)w_up, ids, (float*)inner, C, F, top, act, gated, in_weights);
   } else if (dtype == DT_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(moe_up_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, stream, (const bf16*)h, ldh, (const bf16*)w_up,
-               ids, (bf16*)inner, C, F, top, act);
+               ids, (bf16*)inner, C, F, top, act, gated, in_weights);
   } else {
     return NIB_ERR_BAD_ARGUMENT;
   }
@@ -359,6 +428,27 @@ extern "C" int nib_moe_down(int dtype, const void* inner, const void* w_down, co
   } else {
     return NIB_ERR_BAD_ARGUMENT;
   }
+  NIB_LAUNCH_CHECK();
+}
+
+// pre: [T, n_expert * 2F] in `pre_dtype` (32-bit floats or `dtype`); inner [T, n_expert * F] in `dtype`.
+extern "C" int nib_moe_gate_scale(int pre_dtype, int dtype, const void* pre, void* inner, const int* ids,
+                                  const float* weights, int T, int n_expert, int F, int top, int act, int on_input,
+                                  cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const size_t n = (size_t)T * n_expert * F;
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (pre_dtype == DT_F32 && dtype == DT_F32)
+    launch_pdl(moe_gate_scale_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)pre, (float*)inner, ids,
+               weights, n_expert, F, top, act, on_input, n);
+  else if (pre_dtype == DT_F32 && dtype == DT_BF16)
+    launch_pdl(moe_gate_scale_kernel<float, bf16>, grid, dim3(256), 0, stream, (const float*)pre, (bf16*)inner, ids,
+               weights, n_expert, F, top, act, on_input, n);
+  else if (pre_dtype == DT_BF16 && dtype == DT_BF16)
+    launch_pdl(moe_gate_scale_kernel<bf16, bf16>, grid, dim3(256), 0, stream, (const bf16*)pre, (bf16*)inner, ids,
+               weights, n_expert, F, top, act, on_input, n);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();
 }
 

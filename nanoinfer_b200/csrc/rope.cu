@@ -1,0 +1,117 @@
+// Rotary positions on queries and keys, fused with what follows the q/k/v projection of an attention layer:
+// the cast to the engine's dtype, the padding of a head to the cache's head size, and the append of keys and
+// values to their slots of the paged cache.
+//
+// A head's first `rot_dims` values turn in pairs (2i, 2i + 1) (the interleaved layout) by the angle
+// a = position * freqs[i]:   (u, w) -> (u cos a - w sin a, w cos a + u sin a);   the other values pass.
+// The angle and its sine and cosine are made in double precision from a table of frequencies that the host
+// computed in double precision, so that a position of many thousands loses nothing.
+//
+// proj [T, ld] float: a row holds [q: n_head x dim | k: n_kv_head x dim | v: n_kv_head x vdim] at q_off, k_off,
+// v_off.  q_out [T, ldq] receives n_head heads of `hd` values (dim values, then zeros); the cache layer
+// [n_pages, 2, n_kv_head, page_size, hd] receives the row's keys (plane 0) and values (plane 1), padded
+// likewise.  Rows of no request (row_entry < 0) write their queries only.  A block a row; a thread owns pair i of
+// every n-th head.
+#include "api.h"
+#include "common.cuh"
+
+namespace nib {
+
+template <typename T>
+__device__ __forceinline__ void store_pair(T* p, float a, float b);
+template <>
+__device__ __forceinline__ void store_pair<float>(float* p, float a, float b) {
+  *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+template <>
+__device__ __forceinline__ void store_pair<bf16>(bf16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_append_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, int n_head, int n_kv_head, int dim,
+                   int vdim, int hd, int rot_dims, const double* __restrict__ freqs, const int* __restrict__ positions,
+                   const int* __restrict__ row_entry, T* q_out, int ldq, T* cache, const int* __restrict__ block_table,
+                   int max_blocks, int page_size, int n_pages, int* status) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int pos = positions[t], entry = row_entry[t];
+  T* k_dst = nullptr;
+  T* v_dst = nullptr;
+  if (entry >= 0 && cache != nullptr) {
+    const int page = block_table[(size_t)entry * max_blocks + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+      if (threadIdx.x == 0) *status = NIB_STATUS_BAD_PAGE;
+    } else {
+      k_dst = cache + kv_offset(page, 0, 0, pos % page_size, n_kv_head, page_size, hd);
+      v_dst = cache + kv_offset(page, 1, 0, pos % page_size, n_kv_head, page_size, hd);
+    }
+  }
+  const size_t head_stride = (size_t)page_size * hd;   // from one key/value head's row to the next head's
+  pdl_wait();
+  const float* p = proj + (size_t)t * ld;
+  // a thread owns pair i of every n-th head (queries, then keys, then values), n = groups of hd / 2 threads a block
+  const int half = hd / 2, i = threadIdx.x % half, group = threadIdx.x / half, n_groups = blockDim.x / half;
+  if (group >= n_groups) return;
+  float c = 1.0f, s = 0.0f;
+  if (2 * i < rot_dims) {
+    double sd, cd;
+    sincos((double)pos * freqs[i], &sd, &cd);
+    c = (float)cd;
+    s = (float)sd;
+  }
+  const bool in_k = 2 * i < dim, in_v = 2 * i < vdim;
+  for (int hh = group; hh < n_head + 2 * n_kv_head; hh += n_groups) {
+    if (hh < n_head + n_kv_head) {             // a query or a key head: rotated
+      const bool is_q = hh < n_head;
+      const int h = is_q ? hh : hh - n_head;
+      if (!is_q && k_dst == nullptr) continue;
+      float u = 0.0f, w = 0.0f;
+      if (in_k) {
+        const float2 x = *reinterpret_cast<const float2*>(p + (is_q ? q_off : k_off) + h * dim + 2 * i);
+        u = x.x * c - x.y * s;
+        w = x.y * c + x.x * s;
+      }
+      store_pair<T>(is_q ? q_out + (size_t)t * ldq + h * hd + 2 * i : k_dst + h * head_stride + 2 * i, u, w);
+    } else if (v_dst != nullptr) {
+      const int h = hh - n_head - n_kv_head;
+      float2 y = make_float2(0.0f, 0.0f);
+      if (in_v) y = *reinterpret_cast<const float2*>(p + v_off + h * vdim + 2 * i);
+      store_pair<T>(v_dst + h * head_stride + 2 * i, y.x, y.y);
+    }
+  }
+}
+
+}  // namespace nib
+
+using namespace nib;
+
+// dim, vdim, hd, rot_dims, ld, ldq and the three offsets even; rot_dims <= dim <= hd, vdim <= hd; freqs holds
+// rot_dims / 2 values (may be null when rot_dims is 0); cache may be null (queries only).
+extern "C" int nib_rope_append(int dtype, const float* proj, int ld, int q_off, int k_off, int v_off, int n_head,
+                               int n_kv_head, int dim, int vdim, int hd, int rot_dims, const double* freqs,
+                               const int* positions, const int* row_entry, void* q_out, int ldq, void* cache,
+                               const int* block_table, int max_blocks, int page_size, int n_pages, int T, int* status,
+                               cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((dim | vdim | hd | rot_dims | ld | ldq | q_off | k_off | v_off) & 1) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (dim <= 0 || vdim <= 0 || dim > hd || vdim > hd || rot_dims < 0 || rot_dims > dim) return NIB_ERR_BAD_ARGUMENT;
+  if (rot_dims > 0 && freqs == nullptr) return NIB_ERR_BAD_ARGUMENT;
+  if (hd / 2 > 256) return NIB_ERR_UNSUPPORTED_SIZE;
+  const int per = hd / 2, total = n_head + 2 * n_kv_head;
+  int groups = 256 / per;
+  if (groups > total) groups = total;
+  const dim3 block(groups * per);
+  if (dtype == DT_F32)
+    launch_pdl(rope_append_kernel<float>, dim3(T), block, 0, stream, proj, ld, q_off, k_off, v_off, n_head, n_kv_head,
+               dim, vdim, hd, rot_dims, freqs, positions, row_entry, (float*)q_out, ldq, (float*)cache, block_table,
+               max_blocks, page_size, n_pages, status);
+  else if (dtype == DT_BF16)
+    launch_pdl(rope_append_kernel<bf16>, dim3(T), block, 0, stream, proj, ld, q_off, k_off, v_off, n_head, n_kv_head,
+               dim, vdim, hd, rot_dims, freqs, positions, row_entry, (bf16*)q_out, ldq, (bf16*)cache, block_table,
+               max_blocks, page_size, n_pages, status);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
+  NIB_LAUNCH_CHECK();
+}

@@ -11,6 +11,10 @@
 //   rmsnorm      : out[r] = x[rows[r]] / sqrt(mean + eps) * w   (the model's last norm, wanted rows only)
 //   act          : tanh, or xIELU with its two numbers p, q read from the device:
 //                  z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2
+// and for layers that normalise a sublayer's output before the sum as well as its input:
+//   add_norm     : x += y / sqrt(mean(y^2) + eps) * w_out;  y = 0 (the next sublayer adds its products into it);
+//                  xn = cast(x / sqrt(mean(x^2) + eps) * w_next)   (optional: the next sublayer's input)
+//   glu          : out[t, f] = act(pre[t, 2f]) * pre[t, 2f + 1] (* sigmoid(pre[t, row_gate]) if asked for)
 // Statistics, sums and the activation's arithmetic are 32-bit.
 #include "api.h"
 #include "common.cuh"
@@ -81,6 +85,52 @@ post_norm_kernel(float* x, const float* __restrict__ w, float eps, float* levels
     if (xn != nullptr) xn[base + c] = from_float<OutT>(z);
     x[base + c] = alpha_next * z;
   }
+}
+
+// One kernel between two sublayers: the norm of what the last one made, the sum, and the norm that the next one reads.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+add_norm_kernel(float* x, float* y, const float* __restrict__ w_out, const float* __restrict__ w_next, float eps,
+                OutT* xn, int C) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ float smem[];
+  float* row = smem;
+  float* scratch = smem + C;
+  const size_t base = (size_t)blockIdx.x * C;
+  float q = 0.0f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float v = y[base + c];
+    y[base + c] = 0.0f;
+    row[c] = v;
+    q += v * v;
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(q, scratch) / (float)C + eps);
+  float q2 = 0.0f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float v = x[base + c] + row[c] * rstd * w_out[c];
+    x[base + c] = v;
+    row[c] = v;
+    q2 += v * v;
+  }
+  if (w_next == nullptr) return;
+  const float rstd2 = 1.0f / sqrtf(block_sum(q2, scratch) / (float)C + eps);
+  for (int c = threadIdx.x; c < C; c += blockDim.x) xn[base + c] = from_float<OutT>(row[c] * rstd2 * w_next[c]);
+}
+
+// pre [T, ld]: pairs (gate, value) side by side, F of them; row_gate >= 0: one more column whose sigmoid scales the row
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(256)
+glu_kernel(const InT* pre, int ld, OutT* out, int ldo, int n_rows, int F, int act, int row_gate) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_rows * F) return;
+  const int t = (int)(i / F), f = (int)(i % F);
+  const InT* p = pre + (size_t)t * ld;
+  float v = apply_act(to_float(p[2 * f]), act) * to_float(p[2 * f + 1]);
+  if (row_gate >= 0) v *= 1.0f / (1.0f + expf(-to_float(p[row_gate])));
+  out[(size_t)t * ldo + f] = from_float<OutT>(v);
 }
 
 enum : int { UNARY_TANH = 1, UNARY_XIELU = 2 };
@@ -165,6 +215,45 @@ extern "C" int nib_post_norm(int out_dtype, float* x, const float* w, float eps,
   } else {
     return NIB_ERR_BAD_ARGUMENT;
   }
+  NIB_LAUNCH_CHECK();
+}
+
+extern "C" int nib_add_norm(int out_dtype, float* x, float* y, const float* w_out, const float* w_next, float eps,
+                            void* xn, int n_rows, int C, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (C <= 0 || C > 48000) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (w_next != nullptr && xn == nullptr) return NIB_ERR_BAD_ARGUMENT;
+  const size_t smem = (size_t)(C + 32) * sizeof(float);
+  const int threads = C >= 1024 ? 256 : 128;
+  if (out_dtype == DT_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(add_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, y, w_out, w_next, eps, (float*)xn, C);
+  } else if (out_dtype == DT_BF16) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(add_norm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, stream, x, y, w_out, w_next, eps, (bf16*)xn, C);
+  } else {
+    return NIB_ERR_BAD_ARGUMENT;
+  }
+  NIB_LAUNCH_CHECK();
+}
+
+// act: an activation code of the linear epilogues, applied to the gate of each pair.
+extern "C" int nib_glu(int in_dtype, int out_dtype, const void* pre, int ld, void* out, int ldo, int n_rows, int F,
+                       int act, int row_gate, cudaStream_t stream) {
+  if (n_rows <= 0 || F <= 0) return 0;
+  const size_t n = (size_t)n_rows * F;
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (in_dtype == DT_F32 && out_dtype == DT_F32)
+    launch_pdl(glu_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)pre, ld, (float*)out, ldo, n_rows, F,
+               act, row_gate);
+  else if (in_dtype == DT_F32 && out_dtype == DT_BF16)
+    launch_pdl(glu_kernel<float, bf16>, grid, dim3(256), 0, stream, (const float*)pre, ld, (bf16*)out, ldo, n_rows, F,
+               act, row_gate);
+  else if (in_dtype == DT_BF16 && out_dtype == DT_BF16)
+    launch_pdl(glu_kernel<bf16, bf16>, grid, dim3(256), 0, stream, (const bf16*)pre, ld, (bf16*)out, ldo, n_rows, F,
+               act, row_gate);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();
 }
 

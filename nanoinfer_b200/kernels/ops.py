@@ -14,8 +14,10 @@ import torch
 
 from . import build as _build
 
-ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
-ACT_CODES = {None: ACT_NONE, "none": ACT_NONE, "tanh": ACT_GELU_TANH, "erf": ACT_GELU_ERF}
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU_SQ, ACT_SILU = 0, 1, 2, 3, 4
+#: (the products' epilogues take all but "silu", which the element-wise and expert kernels apply)
+ACT_CODES = {None: ACT_NONE, "none": ACT_NONE, "tanh": ACT_GELU_TANH, "erf": ACT_GELU_ERF, "relu2": ACT_RELU_SQ,
+             "silu": ACT_SILU}
 UNARY_TANH, UNARY_XIELU = 1, 2
 
 STATUS_OK, STATUS_BAD_PAGE, STATUS_WAIT_TIMEOUT = 0, 1, 2
@@ -31,7 +33,7 @@ _lib = None
 _c_int, _c_float, _c_ptr = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
 _SIGNATURES = {
-    "nib_embed": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+    "nib_embed": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr],
     "nib_layernorm": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr],
     "nib_kv_append": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr,
                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
@@ -54,20 +56,20 @@ _SIGNATURES = {
                           _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_attention_prefill_tc_supported": [_c_int, _c_int],
     "nib_attention_prefill_tc": [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr,
-                                 _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
+                                 _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
-                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
+                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_attention_decode": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
-                             _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                             _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
                              _c_int, _c_ptr, _c_ptr, _c_ptr],
     "nib_attention_decode_mma_supported": [_c_int, _c_int],
     "nib_attention_decode_mma_clusters": [_c_int, _c_int],
     "nib_attention_decode_mma": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
-                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int,
                                  _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
     "nib_attention_prefill_supported": [_c_int],
     "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
-                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
+                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_convert": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_ptr],
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
@@ -89,8 +91,20 @@ _SIGNATURES = {
     "nib_delta_rule": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
                        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int,
                        _c_ptr, _c_ptr],
-    "nib_moe_route": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
-    "nib_moe_up": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "nib_moe_route": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr,
+                      _c_ptr],
+    "nib_moe_up": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                   _c_ptr, _c_ptr],
+    "nib_moe_gate_scale": [_c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                           _c_int, _c_ptr],
+    "nib_add_norm": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_ptr],
+    "nib_glu": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "nib_rope_append": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                        _c_ptr],
+    "nib_mlstm": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_float,
+                  _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr,
+                  _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr],
     "nib_moe_down": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_scale": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_grouped": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
@@ -236,8 +250,8 @@ def _i32(t: torch.Tensor, name: str) -> None:
 # ------------------------------------------------------------------------------ ops
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
           pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
-          feedback: Optional[torch.Tensor] = None) -> None:
-    """out[t] = table[tokens[t]] (+ pos_table[positions[t]]), written as 32-bit floats.  A negative
+          feedback: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """out[t] = table[tokens[t]] * scale (+ pos_table[positions[t]]), written as 32-bit floats.  A negative
     token -(s + 1) stands for ``feedback[s]``, the token that the step before left on the device for
     slot s."""
     T, C = tokens.shape[0], table.shape[1]
@@ -253,7 +267,7 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
     if tracing():
         _note("embed", "embed", (T, C, 0), T * C, T * C * ((2 if pos_table is not None else 1) * table.element_size() + 4))
     _check(library().nib_embed(_dt(table), _ptr(tokens), _ptr(positions), _ptr(table), _ptr(pos_table),
-                               _ptr(feedback), _ptr(out), T, C, _stream()), "embed")
+                               _ptr(feedback), _ptr(out), T, C, float(scale), _stream()), "embed")
 
 
 def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float, out: torch.Tensor,
@@ -596,7 +610,7 @@ def kv_append(src: torch.Tensor, k_off: int, v_off: int, cache: torch.Tensor, bl
 
 def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                    row_entry: torch.Tensor, positions: torch.Tensor, T: int, n_head: int, scale: float,
-                   window: int, status: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+                   window: int, status: torch.Tensor, rows: Optional[torch.Tensor] = None, sink: bool = False) -> None:
     """Causal attention of T rows of q ([*, n_head * head_dim], any row stride) over one cache layer, with
     the general kernel (any head size up to 256, any page size).  ``rows`` lists the rows to process."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
@@ -605,7 +619,7 @@ def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bloc
     _check(library().nib_attention_simt(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(out), out.stride(0),
                                         _ptr(block_table), block_table.shape[1], _ptr(rows), _ptr(row_entry),
                                         _ptr(positions), T, n_head, n_kv_head, head_dim, page_size, n_pages,
-                                        float(scale), int(window), _ptr(status), _stream()),
+                                        float(scale), int(window), int(sink), _ptr(status), _stream()),
            "attention_simt")
 
 
@@ -702,7 +716,7 @@ def attention_decode_reserve(workspace, n_head: int, head_dim: int) -> None:
 def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                      row_entry: torch.Tensor, positions: torch.Tensor, n_rows: int, n_head: int, scale: float,
                      window: int, status: torch.Tensor, max_keys: int, workspace,
-                     rows: Optional[torch.Tensor] = None) -> None:
+                     rows: Optional[torch.Tensor] = None, sink: bool = False) -> None:
     """Split-KV attention for rows that are single decoded tokens.  ``max_keys``: the longest key
     range among them; partial results go through ``workspace``.  bfloat16 with a head size of 32, 64,
     96 or 128 runs on the warp-level MMA kernel, everything else (and float32, in true 32-bit
@@ -735,8 +749,8 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
         _check(library().nib_attention_decode_mma(_ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),
                                                   out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
                                                   _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head,
-                                                  head_dim, page_size, n_pages, float(scale), int(window), chunk,
-                                                  n_splits, _ptr(counters), _ptr(status),
+                                                  head_dim, page_size, n_pages, float(scale), int(window), int(sink),
+                                                  chunk, n_splits, _ptr(counters), _ptr(status),
                                                   int(n_splits in DECODE_CLUSTER_SPLITS),
                                                   decode_ring_stages(n_rows * n_head, n_splits, head_dim), _stream()),
                "attention_decode_mma")
@@ -744,13 +758,14 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
     _check(library().nib_attention_decode(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),
                                           out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
                                           _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head, head_dim,
-                                          page_size, n_pages, float(scale), int(window), chunk, n_splits,
+                                          page_size, n_pages, float(scale), int(window), int(sink), chunk, n_splits,
                                           _ptr(counters), _ptr(status), _stream()), "attention_decode")
 
 
 def attention_prefill_tc(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                          tiles: torch.Tensor, n_tiles: int, entry_start: torch.Tensor, entry_pos0: torch.Tensor,
-                         n_rows: int, n_head: int, scale: float, window: int, status: torch.Tensor) -> None:
+                         n_rows: int, n_head: int, scale: float, window: int, status: torch.Tensor,
+                         sink: bool = False) -> None:
     """tcgen05 attention for prompt portions (bfloat16, head size 64): ``tiles`` holds (entry, first
     row within the entry) pairs of 128 rows each; ``q`` holds the step's ``n_rows`` rows."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
@@ -761,13 +776,13 @@ def attention_prefill_tc(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
     _check(library().nib_attention_prefill_tc(_ptr(q), q.stride(0), n_rows, _ptr(cache), _ptr(out), out.stride(0),
                                               _ptr(block_table), block_table.shape[1], _ptr(tiles), n_tiles,
                                               _ptr(entry_start), _ptr(entry_pos0), n_head, n_kv_head, head_dim,
-                                              page_size, n_pages, float(scale), int(window), _ptr(status),
+                                              page_size, n_pages, float(scale), int(window), int(sink), _ptr(status),
                                               _stream()), "attention_prefill_tc")
 
 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                       tiles: torch.Tensor, n_tiles: int, entry_start: torch.Tensor, entry_pos0: torch.Tensor,
-                      n_head: int, scale: float, window: int, status: torch.Tensor) -> None:
+                      n_head: int, scale: float, window: int, status: torch.Tensor, sink: bool = False) -> None:
     """Tiled tensor-core attention for prompt portions: ``tiles`` holds (entry, first row within the
     entry) pairs of 64 rows each."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
@@ -776,13 +791,14 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, b
     _check(library().nib_attention_prefill(_ptr(q), q.stride(0), _ptr(cache), _ptr(out), out.stride(0),
                                            _ptr(block_table), block_table.shape[1], _ptr(tiles), n_tiles,
                                            _ptr(entry_start), _ptr(entry_pos0), n_head, n_kv_head, head_dim,
-                                           page_size, n_pages, float(scale), int(window), _ptr(status), _stream()),
-           "attention_prefill")
+                                           page_size, n_pages, float(scale), int(window), int(sink), _ptr(status),
+                                           _stream()), "attention_prefill")
 
 
 def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
-              n_head: int, scale: float, window: int, plan) -> None:
-    """Causal attention of the step's rows over one cache layer.  ``ctx`` is the step's StepContext,
+              n_head: int, scale: float, window: int, plan, sink: bool = False) -> None:
+    """Causal attention of the step's rows over one cache layer.  ``sink``: the softmax's denominator has
+    one more term, exp(0) (a key of score 0 that has no value; every kernel adds it where it divides).  ``ctx`` is the step's StepContext,
     ``plan`` says which rows are single decoded tokens and how the prompt portions are cut into
     tiles (``parts.attention.AttentionPlan``).  Single decoded tokens go to the split-KV kernel;
     prompt portions go to the tiled tensor-core kernels in bfloat16 (head sizes 16..128 in steps of
@@ -795,7 +811,7 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
             _note_attention(ctx.n_rows, plan.decode_keys + plan.prefill_keys, plan.decode_keys + plan.prefill_kv_rows,
                             n_head, n_kv_head, head_dim, q.element_size())
         attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, ctx.n_rows, n_head, scale,
-                       window, ctx.status)
+                       window, ctx.status, sink=sink)
         return
     if plan.n_decode:
         keys = plan.max_decode_keys if window <= 0 else min(plan.max_decode_keys, window)
@@ -803,26 +819,26 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
             _note_attention(plan.n_decode, plan.decode_keys, plan.decode_keys, n_head, n_kv_head, head_dim,
                             q.element_size())
         attention_decode(q, cache, out, block_table, ctx.row_entry, ctx.positions, plan.n_decode, n_head, scale,
-                         window, ctx.status, keys, ctx.workspace, plan.decode_rows)
+                         window, ctx.status, keys, ctx.workspace, plan.decode_rows, sink=sink)
     if plan.n_prefill_rows:
         if traced:
             _note_attention(plan.n_prefill_rows, plan.prefill_keys, plan.prefill_kv_rows, n_head, n_kv_head, head_dim,
                             q.element_size())
-        if q.dtype == torch.bfloat16 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
+        if q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 \
                 and out.data_ptr() % 16 == 0:
             attention_prefill_tc(q, cache, out, block_table, plan.wide_tiles, plan.n_wide_tiles, ctx.entry_start,
-                                 ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status)
-        elif q.dtype == torch.bfloat16 and _can("nib_attention_prefill_supported", head_dim) \
+                                 ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status, sink=sink)
+        elif q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
             attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
-                              n_head, scale, window, ctx.status)
+                              n_head, scale, window, ctx.status, sink=sink)
         else:
             # (portions alone: all of the step's rows, those of no request among them, which the kernel leaves out;
             # the launch then depends on the step's shape only, as a graph needs it)
             attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions,
                            plan.n_prefill_rows if plan.n_decode else ctx.n_rows, n_head, scale, window, ctx.status,
-                           plan.prefill_rows)
+                           plan.prefill_rows, sink=sink)
 
 
 _SRC_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
@@ -1079,23 +1095,30 @@ def delta_rule(proj: torch.Tensor, offsets, wl: torch.Tensor, w0: torch.Tensor, 
 
 # ------------------------------------------------------------------------------ routed experts
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, T: int, top: int, renorm: bool, ids: torch.Tensor,
-              weights: torch.Tensor) -> None:
-    """Router logits in 32-bit, softmax over all experts, the ``top`` largest (ties to the lower index) into
-    ``ids`` int32 [T, top] with their scores in ``weights`` float32 [T, top] (divided by their sum with ``renorm``)."""
+              weights: torch.Tensor, score: str = "softmax") -> None:
+    """Router logits in 32-bit, scores = softmax over all experts (or, ``score`` "sigmoid", each logit's sigmoid),
+    the ``top`` largest (ties to the lower index) into ``ids`` int32 [T, top] with their scores in ``weights``
+    float32 [T, top] (divided by their sum with ``renorm``)."""
+    if score not in ("softmax", "sigmoid"):
+        raise KernelError("moe_route: score is 'softmax' or 'sigmoid'")
     E, C = w_router.shape
     if h.dtype != w_router.dtype or h.stride(1) != 1 or not w_router.is_contiguous():
         raise KernelError("moe_route: h and the router share a dtype")
     _i32(ids, "ids"); _f32(weights, "moe_route: weights")
     if tracing():
         _note("matmul", "router", (T, C, E), 2.0 * T * C * E, (E + T) * C * h.element_size() + 8.0 * T * top)
-    _check(library().nib_moe_route(_dt(h), _ptr(h), h.stride(0), _ptr(w_router), T, C, E, top, int(renorm), _ptr(ids),
-                                   _ptr(weights), _stream()), "moe_route")
+    _check(library().nib_moe_route(_dt(h), _ptr(h), h.stride(0), _ptr(w_router), T, C, E, top, int(renorm),
+                                   int(score == "sigmoid"), _ptr(ids), _ptr(weights), _stream()), "moe_route")
 
 
 def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, inner: torch.Tensor, T: int, top: int,
-           act: int) -> None:
-    """inner[t * top + k] = act(w_up[ids[t, k]] . h[t]) for w_up [experts, F, C]."""
+           act: int, gated: bool = False, in_weights: Optional[torch.Tensor] = None) -> None:
+    """inner[t * top + k] = act(w_up[ids[t, k]] . h[t]) for w_up [experts, F, C].  ``gated``: w_up is
+    [experts, 2F, C] with rows 2f and 2f + 1 the gate and the value of output f, and inner = act(s g) * (s u) with
+    s = in_weights[t, k] (None: 1)."""
     E, F, C = w_up.shape
+    if gated:
+        F //= 2
     if h.dtype != w_up.dtype or inner.dtype != h.dtype or not w_up.is_contiguous() or not inner.is_contiguous() \
             or inner.shape[1] != F:
         raise KernelError("moe_up: h, w_up and inner share a dtype; inner contiguous [T * top, F]")
@@ -1103,12 +1126,13 @@ def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, inner: torch.
         _note("moe", "experts_up", (T * top, C, F), 2.0 * T * top * C * F,
               h.element_size() * (min(E, T * top) * F * C + T * C + T * top * F))
     _check(library().nib_moe_up(_dt(h), _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), _ptr(inner), T, C, F, top,
-                                int(act), _stream()), "moe_up")
+                                int(act), int(gated), _ptr(in_weights), _stream()), "moe_up")
 
 
-def moe_down(inner: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor,
-             T: int, top: int) -> None:
-    """x[t] += sum_k weights[t, k] * w_down[ids[t, k]] . inner[t * top + k] for w_down [experts, C, F]."""
+def moe_down(inner: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: Optional[torch.Tensor],
+             x: torch.Tensor, T: int, top: int) -> None:
+    """x[t] += sum_k weights[t, k] * w_down[ids[t, k]] . inner[t * top + k] for w_down [experts, C, F] (weights
+    None: all 1)."""
     E, C, F = w_down.shape
     _f32(x, "moe_down: x")
     if inner.dtype != w_down.dtype or not w_down.is_contiguous() or not inner.is_contiguous() or x.shape[1] != C:
@@ -1145,21 +1169,50 @@ def moe_scale(inner_all: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
                                    _stream()), "moe_scale")
 
 
+def moe_gate_scale(pre: torch.Tensor, inner_all: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, T: int,
+                   n_expert: int, F: int, top: int, act: int, on_input: bool) -> None:
+    """pre [T, n_expert * 2F] holds every expert's (gate, value) pairs; inner_all [T, n_expert * F] = act(s g) * (s u)
+    (``on_input``) or s * act(g) * u, s the row's weight for the expert, 0 where the row did not choose it."""
+    if not pre.is_contiguous() or not inner_all.is_contiguous() or pre.shape[1] != 2 * n_expert * F \
+            or inner_all.shape[1] != n_expert * F:
+        raise KernelError("moe_gate_scale: pre contiguous [T, experts * 2F], inner_all contiguous [T, experts * F]")
+    if tracing():
+        _note("other", "experts_gate", (T, n_expert * F, 0), 4.0 * T * n_expert * F,
+              T * n_expert * F * (2.0 * pre.element_size() + inner_all.element_size()))
+    _check(library().nib_moe_gate_scale(_dt(pre), _dt(inner_all), _ptr(pre), _ptr(inner_all), _ptr(ids), _ptr(weights),
+                                        T, n_expert, F, top, int(act), int(on_input), _stream()), "moe_gate_scale")
+
+
 def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                inner: torch.Tensor, x: torch.Tensor, T: int, top: int, act: int, workspace) -> None:
+                inner: torch.Tensor, x: torch.Tensor, T: int, top: int, act: int, workspace, gated: bool = False,
+                weight_on_input: bool = False) -> None:
     """x[t] += sum_k weights[t, k] * W_down[ids[t, k]] . act(W_up[ids[t, k]] . h[t]) with w_up [experts, F, C] and
     w_down [experts, C, F].  Steps of few rows: row by row.  Steps of many rows: all experts through the engine's
     own products with the unchosen ones scaled to zero in between (``moe_dense_pays``: the first matrices as one
     product, the second ones a product an expert, all adding into the stream), else expert by expert (weights
     staged in shared memory, a fixed order of additions)."""
     E, F, C = w_up.shape
+    if gated:
+        # w_up [experts, 2F, C]: rows 2f, 2f + 1 the gate and the value of output f.  With ``weight_on_input`` the
+        # score scales both products' results before the activation (the first product is linear) and the
+        # second product runs unweighted.
+        F //= 2
+    elif weight_on_input:
+        raise KernelError("moe_experts: weight_on_input is built for gated experts")
     if tuple(w_down.shape) != (E, C, F):
         raise KernelError("moe_experts: w_down must be [experts, C, F]")
+    in_w = weights if weight_on_input else None
+    out_w = None if weight_on_input else weights
     if moe_dense_pays(T, top, E):
         inner_all = workspace.get("moe.inner_all", (x.shape[0], E * F), h.dtype)
         trace_scope(_rec.layer if _rec is not None else -1, "experts_up")
-        linear(h, w_up.view(E * F, C), None, inner_all, T, act=act)
-        moe_scale(inner_all, ids, weights, T, E, F, top)
+        if gated:
+            pre = workspace.get("moe.pre_all", (x.shape[0], E * 2 * F), torch.float32)
+            linear(h, w_up.view(E * 2 * F, C), None, pre, T)
+            moe_gate_scale(pre, inner_all, ids, weights, T, E, F, top, act, weight_on_input)
+        else:
+            linear(h, w_up.view(E * F, C), None, inner_all, T, act=act)
+            moe_scale(inner_all, ids, weights, T, E, F, top)
         trace_scope(_rec.layer if _rec is not None else -1, "experts_down")
         for e in range(E):
             linear(inner_all[:, e * F:(e + 1) * F], w_down[e], None, x, T, residual=True)
@@ -1168,8 +1221,8 @@ def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: 
     fits = all(32 * (K + 2) * es + 4 * K * 16 <= 200 * 1024 for K in (C, F))   # a tile of 32 outputs, four rows a warp
     grouped = MOE_GROUPED and T * top >= MOE_GROUPED_MIN_ROWS_PER_EXPERT * E and fits
     if not grouped:
-        moe_up(h, w_up, ids, inner, T, top, act)
-        moe_down(inner, w_down, ids, weights, x, T, top)
+        moe_up(h, w_up, ids, inner, T, top, act, gated, in_w)
+        moe_down(inner, w_down, ids, out_w, x, T, top)
         return
     _f32(x, "moe_experts: x")
     if h.dtype != w_up.dtype or inner.dtype != h.dtype or not w_up.is_contiguous() or not w_down.is_contiguous() \
@@ -1179,15 +1232,106 @@ def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: 
     if tracing():
         _note("moe", "experts_up", (T * top, C, F), 2.0 * T * top * C * F,
               h.element_size() * (min(E, T * top) * F * C + T * C + T * top * F))
-    _check(lib.nib_moe_grouped(dt, 0, _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), None, _ptr(inner), None, T, top, E,
-                               F, C, int(act), _stream()), "moe_grouped up")
+    if gated:
+        _check(lib.nib_moe_grouped(dt, 3, _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), _ptr(in_w), _ptr(inner), None, T,
+                                   top, E, 2 * F, C, int(act), _stream()), "moe_grouped gated up")
+    else:
+        _check(lib.nib_moe_grouped(dt, 0, _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), None, _ptr(inner), None, T, top,
+                                   E, F, C, int(act), _stream()), "moe_grouped up")
     parts = workspace.get("moe.parts", (T * top, C), torch.float32)
     if tracing():
         _note("moe", "experts_down", (T * top, F, C), 2.0 * T * top * C * F,
               h.element_size() * (min(E, T * top) * F * C + T * top * F) + 4.0 * T * top * C)
-    _check(lib.nib_moe_grouped(dt, 1, _ptr(inner), inner.stride(0), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(parts),
+    _check(lib.nib_moe_grouped(dt, 1, _ptr(inner), inner.stride(0), _ptr(w_down), _ptr(ids), _ptr(out_w), _ptr(parts),
                                None, T, top, E, C, F, 0, _stream()), "moe_grouped down")
     if tracing():
         _note("other", "experts_sum", (T, C, top), T * C * top, 4.0 * T * C * (top + 2))
     _check(lib.nib_moe_grouped(dt, 2, _ptr(parts), 0, None, None, None, None, _ptr(x), T, top, E, C, F, 0, _stream()),
            "moe_grouped sum")
+
+
+# ----------------------------------------------------------------------------- sublayers normed on both sides
+def add_norm(x: torch.Tensor, y: torch.Tensor, w_out: torch.Tensor, eps: float, n_rows: int,
+             w_next: Optional[torch.Tensor] = None, xn: Optional[torch.Tensor] = None) -> None:
+    """x[:n] += y / sqrt(mean(y^2) + eps) * w_out and y[:n] = 0, all in 32-bit; with ``w_next`` also
+    xn[:n] = x / sqrt(mean(x^2) + eps) * w_next in xn's dtype (the next sublayer's input)."""
+    _f32(x, "add_norm: x"); _f32(y, "add_norm: y"); _f32(w_out, "add_norm: w_out")
+    C = x.shape[1]
+    if not x.is_contiguous() or not y.is_contiguous() or y.shape[1] != C or w_out.numel() != C:
+        raise KernelError("add_norm: x and y contiguous [rows, C], the weights [C]")
+    if w_next is not None:
+        _f32(w_next, "add_norm: w_next")
+        if xn is None or not xn.is_contiguous() or xn.shape[1] != C or w_next.numel() != C:
+            raise KernelError("add_norm: xn contiguous [rows, C] with w_next [C]")
+    if tracing():
+        _note("ln", "add_norm", (n_rows, C, 0), 10.0 * n_rows * C,
+              n_rows * C * (16.0 + (xn.element_size() if w_next is not None else 0)))
+    _check(library().nib_add_norm(_dt(xn) if w_next is not None else 0, _ptr(x), _ptr(y), _ptr(w_out), _ptr(w_next),
+                                  float(eps), _ptr(xn) if w_next is not None else None, n_rows, C, _stream()), "add_norm")
+
+
+def glu(pre: torch.Tensor, out: torch.Tensor, n_rows: int, F: int, act: int, row_gate: int = -1) -> None:
+    """out[t, f] = act(pre[t, 2f]) * pre[t, 2f + 1], times sigmoid(pre[t, row_gate]) where ``row_gate`` >= 0."""
+    if pre.stride(1) != 1 or out.stride(1) != 1 or pre.shape[1] < 2 * F or out.shape[1] < F or row_gate >= pre.shape[1]:
+        raise KernelError("glu: pre [rows, >= 2F] and out [rows, >= F], rows contiguous")
+    if tracing():
+        _note("other", "glu", (n_rows, F, 0), 8.0 * n_rows * F, n_rows * F * (2.0 * pre.element_size() + out.element_size()))
+    _check(library().nib_glu(_dt(pre), _dt(out), _ptr(pre), pre.stride(0), _ptr(out), out.stride(0), n_rows, F, int(act),
+                             int(row_gate), _stream()), "glu")
+
+
+def rope_append(proj: torch.Tensor, offsets, n_head: int, n_kv_head: int, dim: int, vdim: int, rot_dims: int,
+                freqs: Optional[torch.Tensor], ctx, q_out: torch.Tensor, cache: Optional[torch.Tensor],
+                block_table: Optional[torch.Tensor]) -> None:
+    """From the 32-bit q/k/v projection ``proj`` (q, k, v at the three column ``offsets``; heads of ``dim``,
+    ``dim`` and ``vdim`` values): rotary positions on the first ``rot_dims`` values of every query and key head
+    (interleaved pairs, angle = position * freqs[i], in double precision), the cast, and the padding of every head
+    to the cache's head size; queries to ``q_out`` [rows, n_head * head size], keys and values to the rows' slots of
+    the cache layer [pages, 2, kv heads, page, head size] (None: queries only)."""
+    _f32(proj, "rope_append: proj")
+    hd = q_out.shape[1] // n_head
+    if cache is not None:
+        n_pages, two, g, page_size, chd = cache.shape
+        if two != 2 or g != n_kv_head or chd != hd or not cache.is_contiguous() or cache.dtype != q_out.dtype:
+            raise KernelError("rope_append: cache must be contiguous [pages, 2, kv heads, page, head size] of q_out's dtype")
+        _i32(block_table, "block_table")
+    else:
+        n_pages, page_size = 0, 1
+    if freqs is not None and freqs.dtype != torch.float64:
+        raise KernelError("rope_append: freqs must be float64")
+    if tracing():
+        n = (n_head + 2 * n_kv_head) * hd
+        _note("kv_write", "rope_kv_write", (ctx.n_rows, n, 0), 6.0 * ctx.n_rows * n, ctx.n_rows * n * (4.0 + q_out.element_size()))
+    _check(library().nib_rope_append(_dt(q_out), _ptr(proj), proj.stride(0), offsets[0], offsets[1], offsets[2], n_head,
+                                     n_kv_head, dim, vdim, hd, rot_dims, _ptr(freqs), _ptr(ctx.positions),
+                                     _ptr(ctx.row_entry), _ptr(q_out), q_out.stride(0), _ptr(cache), _ptr(block_table),
+                                     block_table.shape[1] if block_table is not None else 0, page_size, n_pages,
+                                     ctx.n_rows, _ptr(ctx.status), _stream()), "rope_append")
+
+
+def mlstm_state_floats(dim: int, vdim: int) -> int:
+    """Floats of state per head of the matrix memory: [vdim + 1 columns][dim rounded up to 16], then the running
+    maximum and three unused floats."""
+    return (vdim + 1) * (-(-dim // 16) * 16) + 4
+
+
+def mlstm(proj: torch.Tensor, offsets, bias_i: torch.Tensor, bias_f: torch.Tensor, cap: float, norm_w: torch.Tensor,
+          state: torch.Tensor, ctx, n_head: int, dim: int, vdim: int, eps: float, out: torch.Tensor, workspace) -> None:
+    """The matrix memory over the step's rows, entry by entry in row order, from the 32-bit projections ``proj``
+    (q, k, v, g, input gate, forget gate at the six column ``offsets``); state [slots, n_head *
+    mlstm_state_floats] float32 from and to each entry's slot; out[:, :n_head * vdim] in out's dtype."""
+    _f32(proj, "mlstm: proj"); _f32(state, "mlstm: state"); _f32(norm_w, "mlstm: norm_w")
+    if not state.is_contiguous() or state[0].numel() != n_head * mlstm_state_floats(dim, vdim):
+        raise KernelError("mlstm: state must be contiguous [slots, n_head * mlstm_state_floats(dim, vdim)]")
+    n = proj.shape[0]
+    gates = workspace.get("mlstm.gates", (n, n_head, 4), torch.float32)
+    num = workspace.get("mlstm.num", (n, n_head * vdim), torch.float32)
+    den = workspace.get("mlstm.den", (n, n_head), torch.float32)
+    if tracing():
+        T = ctx.n_rows
+        _note("scan", "mlstm", (T, n_head * dim, n_head * vdim), 6.0 * T * n_head * dim * vdim,
+              4.0 * T * n_head * (2 * dim + 3 * vdim) + 8.0 * ctx.n_entries * n_head * dim * vdim)
+    _check(library().nib_mlstm(_dt(out), _ptr(proj), proj.stride(0), *[int(o) for o in offsets], _ptr(bias_i), _ptr(bias_f),
+                               float(cap), _ptr(norm_w), _ptr(state), _ptr(ctx.entry_start), _ptr(ctx.entry_slot),
+                               ctx.n_entries, ctx.n_rows, n_head, dim, vdim, float(eps), _ptr(gates), _ptr(num),
+                               num.stride(0), _ptr(den), _ptr(out), out.stride(0), _stream()), "mlstm", 3)

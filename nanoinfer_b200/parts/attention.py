@@ -163,3 +163,102 @@ class CausalSelfAttention(Mixer):
         ops.attention(q, cache.layer, att, cache.block_table, ctx, self.n_head, self.scale, self.window, plan)
         ops.trace_scope(ctx.layer, "attn_proj")
         ops.linear(att, p["out_weight"], p.get("out_bias"), x, T, residual=True)
+
+
+def _round_up(n: int, m: int) -> int:
+    return -(-n // m) * m
+
+
+@register_mixer("general_attention")
+class GeneralAttention(CausalSelfAttention):
+    """Causal attention with the projections as separate tensors and without biases, key and value heads of sizes of
+    their own (``head_dim`` for queries and keys, ``v_dim`` for values), grouped key/value heads (query head h reads
+    key/value head h // (n_head / n_kv_head)), an optional rotary position encoding on queries and keys (``position``:
+    a ``rotary_pairs`` part) and an optional **sink**: the softmax's denominator has one more term, exp(0), as if
+    every row also saw a key of score 0 that has no value:  p_j = exp(s_j) / (1 + sum_j exp(s_j)).
+
+    One product makes q, k and v as 32-bit floats; one kernel turns queries and keys by their positions (in 32-bit,
+    angles in double precision), casts, and writes keys and values into the cache.  The cache and the attention
+    kernels know one head size: the larger of the two, rounded up to 16; keys or values of the smaller size are
+    padded with zeros there (a zero adds nothing to a score and a zero value gives a zero output, which the output
+    projection, its matrix padded with zero columns at load, ignores)."""
+
+    def __init__(self, width: int, n_head: int, n_kv_head: int, head_dim: int, v_dim: int, scale: float,
+                 window: int = 0, sink: bool = False, position: Optional[PositionEncoding] = None):
+        if head_dim <= 0 or v_dim <= 0 or head_dim % 2 or v_dim % 2:
+            raise ValueError(f"general_attention: head_dim {head_dim} and v_dim {v_dim} must be positive and even")
+        self.cache_dim = _round_up(max(head_dim, v_dim), 16)
+        super().__init__(width, n_head, n_kv_head, self.cache_dim, scale, window, bias=False, position=position)
+        self.key_dim, self.v_dim, self.sink = int(head_dim), int(v_dim), bool(sink)
+        rot = getattr(position, "dims", 0)
+        if position is not None and (not hasattr(position, "freqs") or rot > self.key_dim):
+            raise ValueError("general_attention: the position encoding must be rotary_pairs with dims <= head_dim")
+        self.n_q, self.n_k, self.n_v = self.n_head * self.key_dim, self.n_kv_head * self.key_dim, self.n_kv_head * self.v_dim
+        #: columns of the fused projection's output (rows of 32-bit floats, a multiple of 8 wide)
+        self.n_proj = _round_up(self.n_q + self.n_k + self.n_v, 8)
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [ParamSpec("q_weight", (self.n_q, self.width), MATRIX), ParamSpec("k_weight", (self.n_k, self.width), MATRIX),
+                ParamSpec("v_weight", (self.n_v, self.width), MATRIX),
+                ParamSpec("out_weight", (self.width, self.n_head * self.v_dim), MATRIX)]
+
+    def kv_spec(self) -> Optional[KVCacheSpec]:
+        return KVCacheSpec(self.n_kv_head, self.cache_dim, self.window)
+
+    def flops_per_key(self) -> float:
+        return 2.0 * self.n_head * (self.key_dim + self.v_dim)
+
+    def prepare(self, dtype, device) -> None:
+        super().prepare(dtype, device)
+        p = self.params
+        # the three products that read the mixer's input are one; the parameters by name become views of it
+        w = torch.zeros(self.n_proj, self.width, dtype=p["q_weight"].dtype, device=p["q_weight"].device)
+        at = 0
+        for key in ("q_weight", "k_weight", "v_weight"):
+            n = p[key].shape[0]
+            w[at:at + n] = p[key]
+            p[key] = w[at:at + n]
+            at += n
+        self.w_qkv = w
+        # the output projection reads heads of the cache's size: zero columns where a value head is shorter
+        if self.v_dim == self.cache_dim:
+            self.w_out = p["out_weight"]
+        else:
+            wo = torch.zeros(self.width, self.n_head, self.cache_dim, dtype=w.dtype, device=w.device)
+            wo[:, :, :self.v_dim] = p["out_weight"].view(self.width, self.n_head, self.v_dim)
+            self.w_out = wo.view(self.width, self.n_head * self.cache_dim)
+            p["out_weight"] = self.w_out.view(self.width, self.n_head, self.cache_dim)[:, :, :self.v_dim]
+
+    def reserve(self, workspace: Workspace, limits: StepLimits) -> None:
+        n = limits.max_rows
+        workspace.reserve("attention.proj32", n * self.n_proj, torch.float32)
+        workspace.reserve("attention.q", n * self.q_dim, self.dtype)
+        workspace.reserve("attention.out", n * self.q_dim, self.dtype)
+        ops.attention_decode_reserve(workspace, self.n_head, self.head_dim)
+
+    def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: Optional[KVCacheView],
+                state: Optional[torch.Tensor], writes_cache: bool = True) -> None:
+        if cache is None:
+            raise ValueError("general_attention needs a paged cache")
+        if isinstance(xn, ops.NormInput):
+            xn = xn.materialise(ctx.n_rows)
+        T, ws = ctx.n_rows, ctx.workspace
+        proj = ws.get("attention.proj32", (ctx.max_rows, self.n_proj), torch.float32)
+        ops.trace_scope(ctx.layer, "qkv")
+        # (a run that reads another run's keys and values projects its queries only)
+        ops.linear(xn, self.w_qkv if writes_cache else self.w_qkv[:self.n_q], None,
+                   proj if writes_cache else proj[:, :self.n_q], T)
+        q = ws.get("attention.q", (ctx.max_rows, self.q_dim), self.dtype)
+        pos = self.position
+        ops.rope_append(proj, (0, self.n_q, self.n_q + self.n_k), self.n_head, self.n_kv_head, self.key_dim, self.v_dim,
+                        pos.dims if pos is not None else 0, pos.freqs if pos is not None else None, ctx, q,
+                        cache.layer if writes_cache else None, cache.block_table if writes_cache else None)
+        att = ws.get("attention.out", (ctx.max_rows, self.q_dim), self.dtype)
+        plan = ctx.plans.get("causal_attention")
+        if plan is None:
+            plan = ctx.plans["causal_attention"] = AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0,
+                                                                 device=x.device)
+        ops.attention(q, cache.layer, att, cache.block_table, ctx, self.n_head, self.scale, self.window, plan,
+                      sink=self.sink)
+        ops.trace_scope(ctx.layer, "attn_proj")
+        ops.linear(att, self.w_out, None, x, T, residual=True)

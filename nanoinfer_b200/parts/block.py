@@ -138,3 +138,58 @@ class PostNormDepthMixBlock(Block):
                       alpha_next=nxt.alpha if fuse else 1.0, levels=levels,
                       n_levels=self.depth_mix.n_levels if levels is not None else 0,
                       mix=self.depth_mix.params["weights"] if levels is not None else None)
+
+
+@register_block("sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm before AND after each sublayer, the second one ahead of the sum:
+        x <- x + norm_1b(mixer(norm_1(x)));   x <- x + norm_2b(feed_forward(norm_2(x)))
+    (a layer without a feed-forward has the first line only).  All four are RMS norms with one eps.
+
+    A sublayer adds its products into a 32-bit buffer of its own that it finds zero.  Between two sublayers runs
+    ONE kernel: the norm of that buffer, the sum into the stream, the buffer zeroed again, and the norm that the
+    next sublayer reads, also the first norm of the next layer where that is of this arrangement
+    (``ctx.stream_entered`` then tells it that its input is ready)."""
+
+    slots = {"norm_1": NORMS, "mixer": MIXERS, "norm_1b": NORMS, "norm_2": NORMS, "feed_forward": FEED_FORWARDS,
+             "norm_2b": NORMS}
+    optional = ("norm_2", "feed_forward", "norm_2b")
+
+    def __init__(self, width: int, parts: Dict[str, Part]):
+        super().__init__(width, parts)
+        have = [name in parts for name in ("norm_2", "feed_forward", "norm_2b")]
+        if any(have) and not all(have):
+            raise ValueError("sandwich_norm: norm_2, feed_forward and norm_2b come together or not at all")
+        norms = [parts[n] for n in ("norm_1", "norm_1b", "norm_2", "norm_2b") if n in parts]
+        if any(not hasattr(n, "eps") or "bias" in {s.key for s in n.param_specs()} for n in norms):
+            raise ValueError("sandwich_norm: its norms must be RMS norms")
+        if len({n.eps for n in norms}) != 1:
+            raise ValueError("sandwich_norm: its norms share one eps")
+        self.eps = norms[0].eps
+        self.norm_2, self.feed_forward, self.norm_2b = parts.get("norm_2"), parts.get("feed_forward"), parts.get("norm_2b")
+
+    def reserve(self, workspace, limits) -> None:
+        workspace.reserve("block.normed", limits.max_rows * self.width, limits.dtype)
+        workspace.reserve("block.sublayer", limits.max_rows * self.width, torch.float32, zeroed=True)
+
+    def forward(self, x, ctx, cache, state, writes_cache, dtype) -> None:
+        T, ws = ctx.n_rows, ctx.workspace
+        xn = ws.get("block.normed", (ctx.max_rows, self.width), dtype)
+        # zero when first handed out, and zeroed again by every kernel that reads it
+        y = ws.get_zeroed("block.sublayer", (ctx.max_rows, self.width), torch.float32)
+        if ctx.stream_entered:
+            ctx.stream_entered = False      # the arrangement before this one left norm_1(x) behind
+        else:
+            self.norm_1.forward(x, xn, T)
+        self.mixer.forward(xn, y, ctx, cache, state, writes_cache)
+        last = self.norm_1b
+        if self.feed_forward is not None:
+            ops.add_norm(x, y, self.norm_1b.params["weight"], self.eps, T, self.norm_2.params["weight"], xn)
+            self.feed_forward.forward(xn, y, ctx)
+            last = self.norm_2b
+        nxt = ctx.next_block
+        fuse = isinstance(nxt, SandwichNormBlock) and nxt.width == self.width and nxt.eps == self.eps
+        if fuse:
+            ctx.stream_entered = True
+        ops.add_norm(x, y, last.params["weight"], self.eps, T, nxt.norm_1.params["weight"] if fuse else None,
+                     xn if fuse else None)

@@ -2,7 +2,8 @@
 (reference: crates/core/src/stages/blocks.rs:113-137).  The reference fixes the inner width
 at 4C (crates/core/src/weights.rs:95-98) and the activation at tanh-GELU
 (crates/core/src/kernels/reference.rs:53-61); both are parameters here, and the exact
-erf-GELU is offered beside the tanh form, and xIELU, an activation with two learned numbers p, q:
+erf-GELU is offered beside the tanh form, the square of relu ("relu2": max(z, 0)^2), and xIELU, an
+activation with two learned numbers p, q:
 z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2."""
 from __future__ import annotations
 
@@ -19,8 +20,9 @@ class DenseMLP(FeedForward):
     takes_norm_input = True
 
     def __init__(self, width: int, inner: int, activation: str, bias: bool = True):
-        if activation not in ("tanh", "erf", "xielu"):
-            raise ValueError(f"activation {activation!r} is not one of 'tanh', 'erf' (the two GELU forms), 'xielu'")
+        if activation not in ("tanh", "erf", "relu2", "xielu"):
+            raise ValueError(f"activation {activation!r} is not one of 'tanh', 'erf' (the two GELU forms), 'relu2', "
+                             "'xielu'")
         self.width, self.inner, self.activation, self.bias = int(width), int(inner), activation, bool(bias)
 
     def param_specs(self) -> List[ParamSpec]:

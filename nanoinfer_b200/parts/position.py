@@ -7,6 +7,7 @@ from typing import List, Optional
 
 import torch
 
+from ..kernels import ops
 from .base import TABLE, ParamSpec, PositionEncoding, register_position
 
 
@@ -23,3 +24,30 @@ class LearnedAbsolutePositions(PositionEncoding):
 
     def max_positions(self) -> Optional[int]:
         return self.n_positions
+
+
+@register_position("rotary_pairs")
+class RotaryPairs(PositionEncoding):
+    """Rotary positions inside a mixer: of every query and key head the first ``dims`` values turn in pairs
+    (2i, 2i + 1) (the interleaved layout) by the angle position * base^(-2i / dims); the other values pass.
+    It has no parameters.  The frequencies are made in double precision on the host; the rotation itself is
+    done by the mixer's own kernel between the projection and the cache (``kernels.ops.rope_append``), which asks
+    this part for ``dims`` and ``freqs``."""
+
+    def __init__(self, base: float, dims: int):
+        if dims < 0 or dims % 2:
+            raise ValueError(f"rotary_pairs: dims {dims} must be even and not negative")
+        if dims and not base > 0.0:
+            raise ValueError(f"rotary_pairs: base {base} must be positive")
+        self.base, self.dims = float(base), int(dims)
+        self.freqs: Optional[torch.Tensor] = None
+
+    def prepare(self, dtype, device) -> None:
+        super().prepare(dtype, device)
+        if self.dims:
+            i = torch.arange(self.dims // 2, dtype=torch.float64)
+            self.freqs = (self.base ** (-2.0 * i / self.dims)).to(device)
+
+    def on_qk(self, q, k, ctx) -> None:
+        raise NotImplementedError("rotary_pairs turns queries and keys inside ops.rope_append, on the projection's "
+                                  "32-bit output; a mixer that holds it calls that")

@@ -76,5 +76,10 @@ def _register_builtin() -> None:
 
     register_architecture("Vadonex", VadonexConfig, build_vadonex_spec)
 
+    from .config.mulavik import MulavikConfig
+    from .models.mulavik import build_mulavik_spec
+
+    register_architecture("Mulavik", MulavikConfig, build_mulavik_spec)
+
 
 _register_builtin()

@@ -291,7 +291,7 @@ def test_both_decode_attention_kernels_at_every_split(dtype, case):
                 continue                     # (beyond the portable cluster size of 8 there is no ring)
             args = (q.data_ptr(), q.stride(0), cache.data_ptr(), scratch.data_ptr(), out.data_ptr(), out.stride(0),
                     table.data_ptr(), table.shape[1], None, ctx.row_entry.data_ptr(), ctx.positions.data_ptr(), n_rows,
-                    n_head, n_kv_head, hd, ps, cache.shape[0], scale, window, chunk, n_splits, counters.data_ptr(),
+                    n_head, n_kv_head, hd, ps, cache.shape[0], scale, window, 0, chunk, n_splits, counters.data_ptr(),
                     ctx.status.data_ptr())
             code = lib.nib_attention_decode(dt, *args, stream) if kernel == "streaming" else \
                 lib.nib_attention_decode_mma(*args, int("cluster" in kernel),
