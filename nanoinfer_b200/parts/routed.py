@@ -16,12 +16,16 @@ before the activation); ``shared_row_gate``: the shared expert's output times si
 """
 from __future__ import annotations
 
-from typing import List
+import itertools
+from typing import List, Optional
 
 import torch
 
 from ..kernels import ops
 from .base import MATRIX, FeedForward, ParamSpec, StepContext, register_feed_forward
+
+
+_instances = itertools.count()
 
 
 @register_feed_forward("routed_experts")
@@ -45,6 +49,10 @@ class RoutedExperts(FeedForward):
         self.activation, self.renorm = activation, bool(renorm)
         self.shared_inner, self.shared_activation = int(shared_inner), shared_activation
         self.score, self.gated, self.weight_on = score, bool(gated), weight_on
+        # every part keeps the experts it chose in a buffer of its own: after a step (replayed from a graph or not)
+        # ``last_ids[:rows]`` says which experts each row of that step went to
+        self._ids_name = f"moe.ids.{next(_instances)}"
+        self.last_ids: Optional[torch.Tensor] = None
         self.shared_row_gate = bool(shared_row_gate)
 
     def param_specs(self) -> List[ParamSpec]:
@@ -102,7 +110,7 @@ class RoutedExperts(FeedForward):
 
     def reserve(self, workspace, limits) -> None:
         n = limits.max_rows
-        workspace.reserve("moe.ids", n * self.top, torch.int32)
+        workspace.reserve(self._ids_name, n * self.top, torch.int32)
         workspace.reserve("moe.weights", n * self.top, torch.float32)
         workspace.reserve("moe.inner", n * self.top * self.inner, self.dtype)
         workspace.reserve("moe.parts", n * self.top * self.width, torch.float32)
@@ -119,7 +127,7 @@ class RoutedExperts(FeedForward):
         if isinstance(xn, ops.NormInput):
             xn = xn.materialise(ctx.n_rows)
         T, p, ws, n = ctx.n_rows, self.params, ctx.workspace, ctx.max_rows
-        ids = ws.get("moe.ids", (n, self.top), torch.int32)
+        ids = self.last_ids = ws.get(self._ids_name, (n, self.top), torch.int32)
         weights = ws.get("moe.weights", (n, self.top), torch.float32)
         ops.trace_scope(ctx.layer, "router")
         ops.moe_route(xn, p["router"], T, self.top, self.renorm, ids, weights, score=self.score)

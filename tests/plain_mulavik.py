@@ -51,7 +51,7 @@ def rotate_pairs(v: torch.Tensor, positions: torch.Tensor, base: float, dims: in
 def sink_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, pos0: int = 0) -> torch.Tensor:
     """Causal attention with grouped key/value heads, rotary positions on part of each head and a softmax
     whose denominator has one more term, exp(0): weights exp(s_j) / (1 + sum_j exp(s_j))."""
-    n, H, G, d, dv = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    n, H, G, d, dv = h.shape[0], m["heads"], m.get("kv_heads") or m["heads"], m["dim"], m["vdim"]
     rot = m.get("rot") or {}
     pos = torch.arange(pos0, pos0 + n)
     q = rotate_pairs((h @ W[p + "q"].T).view(n, H, d), pos, float(rot.get("base", 1.0)), int(rot.get("dims", 0)))
@@ -115,21 +115,42 @@ def gated_expert(h, W: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
     return (silu(h @ W[p + "gate"].T) * (h @ W[p + "up"].T)) @ W[p + "down"].T
 
 
-def routed_ff(h, W: Dict[str, torch.Tensor], p: str, mlp: dict, margins: Optional[list] = None) -> torch.Tensor:
+#: a router's call is close where the last chosen logit leads the first unchosen one by less than this, over the
+#: root mean square of the row's logits
+CLOSE_CALL = 0.03
+
+
+def routed_ff(h, W: Dict[str, torch.Tensor], p: str, mlp: dict, margins: Optional[list] = None,
+              given: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Sigmoid scores, the ``top`` largest chosen, the score multiplies the expert's INPUT; a shared expert
-    for every row, times sigmoid of one number per row."""
+    for every row, times sigmoid of one number per row.  ``given`` [n, top]: choices made elsewhere (in reduced
+    precision); a row whose own call is close follows them, after a check that they differ from its own only by
+    experts whose logits lie that close to the border."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
-    s = torch.sigmoid(h @ W[p + "router"].T)
+    z = h @ W[p + "router"].T
+    s = torch.sigmoid(z)
     order = torch.sort(s, dim=-1, descending=True, stable=True)
     if margins is not None:
+        # by how much the last chosen expert's logit leads the first unchosen one's, over the logits' root mean square
         if top < E:
-            margins.append((order.values[:, top - 1] - order.values[:, top]) / order.values[:, top - 1].clamp_min(1e-30))
+            zs = torch.sort(z, dim=-1, descending=True).values
+            margins.append((zs[:, top - 1] - zs[:, top]) / z.pow(2).mean(-1).sqrt().clamp_min(1e-30))
         else:
             margins.append(torch.full((h.shape[0],), math.inf, dtype=h.dtype))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        for j in range(top):
-            e = int(order.indices[t, j])
+        chosen = [int(e) for e in order.indices[t, :top]]
+        if given is not None and top < E:
+            zs = torch.sort(z[t], descending=True).values
+            rms_z = float(z[t].pow(2).mean().sqrt())
+            if float(zs[top - 1] - zs[top]) < CLOSE_CALL * rms_z:
+                other = [int(e) for e in given[t]]
+                border = float(zs[top - 1] + zs[top]) / 2
+                for e in set(other) ^ set(chosen):
+                    assert abs(float(z[t, e]) - border) <= CLOSE_CALL * rms_z, (t, e, chosen, other)
+                assert len(set(other)) == top
+                chosen = other
+        for e in chosen:
             out[t] += gated_expert(s[t, e] * h[t:t + 1], W, f"{p}e{e}.")[0]
     if mlp.get("shared") is not None:
         out = out + gated_expert(h, W, p + "shared.") * torch.sigmoid(h @ W[p + "shared.sg"].T)
@@ -153,7 +174,7 @@ class PlainMulavik:
         #: after ``logits``: the residual stream behind every layer, [layers, n, width]
         self.streams: Optional[torch.Tensor] = None
 
-    def layer(self, i: int, x: torch.Tensor, margins: list) -> torch.Tensor:
+    def layer(self, i: int, x: torch.Tensor, margins: list, given: Optional[torch.Tensor] = None) -> torch.Tensor:
         W, eps, layer, p = self.W, self.eps, self.cfg["layers"][i], f"l{i}."
         h = rms_norm(x, W[p + "norm1"], eps)
         if layer["type"] == "attention":
@@ -166,19 +187,27 @@ class PlainMulavik:
         mlp = layer.get("mlp")
         if mlp is not None:
             h = rms_norm(x, W[p + "norm2"], eps)
-            y = dense_ff(h, W, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(h, W, p + "mlp.", mlp, margins)
+            y = dense_ff(h, W, p + "mlp.") if mlp["kind"] == "dense" else routed_ff(h, W, p + "mlp.", mlp, margins, given)
             x = x + rms_norm(y, W[p + "norm2b"], eps)
         return x
 
-    def logits(self, tokens: Sequence[int]) -> torch.Tensor:
+    def logits(self, tokens: Sequence[int], choices: Optional[Dict[int, torch.Tensor]] = None) -> torch.Tensor:
+        """``choices``: per routed layer, the experts [n, top] that a reduced-precision run chose; rows whose own
+        call is close follow them (``routed_ff``)."""
         W = self.W
         x = W["embed"][torch.tensor(list(tokens), dtype=torch.long)] * float(self.cfg["embedding"]["scale"])
         margins: List[torch.Tensor] = []
         streams = []
         for i in range(len(self.cfg["layers"])):
-            x = self.layer(i, x, margins)
+            x = self.layer(i, x, margins, None if choices is None else choices.get(i))
             streams.append(x)
         self.streams = torch.stack(streams)
         self.router_margin = (torch.stack(margins).min(0).values if margins
                               else torch.full((len(tokens),), math.inf, dtype=torch.float64))
         return rms_norm(x, W["final.norm"], self.eps) @ W["head"].T
+
+    def greedy(self, prompt: Sequence[int], n_new: int) -> List[int]:
+        toks = list(prompt)
+        for _ in range(n_new):
+            toks.append(int(self.logits(toks)[-1].argmax()))
+        return toks[len(prompt):]
