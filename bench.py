@@ -3,7 +3,7 @@
 weights, bfloat16) at batch 8 on one B200, with prefill, roofline and end-to-end figures.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--preset NAME]
-    python bench.py --compare-designs [--widths 768,1024,1600] [--layers 4]
+    python bench.py --compare-designs [--designs mulavik,vadonex,gpt2] [--widths 768,1024,1600] [--layers 4]
 
 With --compare-designs another line is printed instead: Vadonex (latent attention, delta rule, routed
 experts) beside GPT-2 at equal width, depth, vocabulary and context, prefill and decode throughput and each
@@ -63,6 +63,8 @@ def main() -> int:
     ap.add_argument("--compare-designs", action="store_true",
                     help="Vadonex beside GPT-2 at equal layer sizes instead of the headline workload")
     ap.add_argument("--widths", default="768,1024,1600", help="with --compare-designs: the model widths")
+    ap.add_argument("--designs", default="vadonex,gpt2",
+                    help="with --compare-designs: which of mulavik, vadonex, gpt2 stand side by side")
     ap.add_argument("--preheat", type=float, default=1.5,
                     help="seconds of untimed prefill steps before the timed loops (0: none)")
     args = ap.parse_args()
@@ -82,7 +84,8 @@ def main() -> int:
 
     if args.compare_designs:
         sizes = bs.compare_designs([int(w) for w in args.widths.split(",")], n_layer=args.layers or 4,
-                                   batch=args.batch, steps=min(args.steps, 64), warmup=max(3, args.warmup))
+                                   batch=args.batch, steps=min(args.steps, 64), warmup=max(3, args.warmup),
+                                   designs=tuple(d for d in args.designs.split(",") if d))
         print(json.dumps({"metric": "designs side by side", "dtype": "bf16", "data": "synthetic",
                           "peaks": bs.measured_peaks(), "sizes": sizes, "provenance": bs.provenance()}))
         return 0

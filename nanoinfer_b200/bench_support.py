@@ -427,6 +427,26 @@ def vadonex_like(width: int, n_layer: int, vocab: int, window: int) -> dict:
     return dict(architecture="Vadonex", vocab=vocab, width=width, postln_alpha=2.0, norm=dict(eps=1e-6), layers=layers)
 
 
+def mulavik_like(width: int, n_layer: int, vocab: int) -> dict:
+    """A Mulavik configuration whose layers have the sizes of a GPT-2 of ``width``: by turns a matrix-memory layer
+    (four heads, keys of width / 8 and values of width / 4) with a dense feed-forward of 4 x width, an attention
+    layer (heads of 64, a key/value head for four query heads, half of a head rotated) with routed experts (8 gated
+    experts of the model's width, 2 a row, one shared), a matrix-memory layer with routed experts, and an attention
+    layer with a dense feed-forward."""
+    heads = width // 64
+    kv_heads = max(d for d in range(1, max(1, heads // 4) + 1) if heads % d == 0)   # about four query heads a key head
+    att = dict(heads=heads, kv_heads=kv_heads, dim=64, vdim=64, scale=0.125, rot=dict(base=10000.0, dims=32))
+    mem = dict(heads=4, dim=width // 8, vdim=width // 4, gate_cap=15.0)
+    moe = dict(kind="moe", router=dict(experts=8, top=2), expert=dict(ff=width), shared=dict(ff=width))
+    dense = dict(kind="dense", ff=4 * width)
+    layers = []
+    for i in range(n_layer):
+        mixer, mlp = (("mlstm", mem), ("attention", att))[i % 2], (dense, moe, moe, dense)[i % 4]
+        layers.append(dict(type=mixer[0], mixer=dict(mixer[1]), mlp=dict(mlp)))
+    return dict(architecture="Mulavik", vocab=vocab, width=width, embedding=dict(scale=float(width) ** 0.5),
+                norm=dict(eps=1e-6), layers=layers)
+
+
 def folder_of(raw: dict, seed: int, dtype: torch.dtype) -> str:
     """A folder with seeded random weights of the configuration ``raw`` (made once, in the temporary folder)."""
     from .config.base import architecture_name
@@ -481,17 +501,21 @@ def profile_forward(eng, prompt, batch: int, repeats: int = 3):
 
 
 def compare_designs(widths=(768, 1024, 1600), n_layer: int = 4, batch: int = 8, context: int = 1024,
-                    steps: int = 64, warmup: int = 8) -> List[dict]:
-    """Vadonex beside GPT-2 at equal width, depth, vocabulary and context (random weights, bfloat16): one
-    prompt of ``context - steps - warmup`` tokens in one step, decode at ``batch``, and where the time of
-    each goes op by op with every op's fraction of its roofline (measured peaks)."""
+                    steps: int = 64, warmup: int = 8, designs=("vadonex", "gpt2")) -> List[dict]:
+    """The ``designs`` (of "mulavik", "vadonex", "gpt2") side by side at equal width, depth, vocabulary and
+    context (random weights, bfloat16): one prompt of ``context - steps - warmup`` tokens in one step, decode at
+    ``batch``, and where the time of each goes op by op with every op's fraction of its roofline (measured
+    peaks)."""
     peaks = measured_peaks()
     out = []
     for width in widths:
         gpt2 = dict(architectures=["GPT2LMHeadModel"], vocab_size=50257, n_positions=context, n_embd=width,
                     n_layer=n_layer, n_head=width // 64, layer_norm_epsilon=1e-5, activation_function="gelu_new")
         record = {"width": width, "n_layer": n_layer, "batch": batch, "context": context}
-        for name, raw in (("vadonex", vadonex_like(width, n_layer, 50257, context)), ("gpt2", gpt2)):
+        made = {"vadonex": lambda: vadonex_like(width, n_layer, 50257, context), "gpt2": lambda: gpt2,
+                "mulavik": lambda: mulavik_like(width, n_layer, 50257)}
+        for name in designs:
+            raw = made[name]()
             d = folder_of(raw, 1234, torch.bfloat16)
             eng = build_engine(d, "bfloat16", batch, context, max_rows=2048)
             preheat(eng, 0.5)

@@ -17,19 +17,22 @@
 //                  value is 1 (the first block of a head carries it).  A column lives in the registers of four
 //                  neighbouring threads, which take the 16-byte pieces r, r + 4, r + 8, ... of q and k (the four
 //                  read 64 bytes side by side: no bank conflicts; S^T q is a sum over four lanes, two shuffles).  The
-//                  next row's q, k, v and factors pass through a double buffer in shared memory: one barrier a row.
+//                  rows' q, k, v and factors come into shared memory eight rows at a time by `cp.async`, the next
+//                  eight while these are worked on: two barriers per eight rows, none between rows.
 //                  It leaves the numerators S'^T q and the denominators.
 //   mlstm_finish : a warp per (row, head): the division, the head's root mean square, weight and gate.
 // The projections come in as 32-bit floats; everything here is 32-bit.  State per slot and head:
 // [value channels + 1][dim rounded up to 16] floats (the last column is n), then mx and three unused floats.
+#include <cstdint>
+
 #include "api.h"
 #include "common.cuh"
 
 namespace nib {
 
-constexpr int ML_VC = 64;                 // value channels a block
-constexpr int ML_THREADS = 4 * (ML_VC + 8);   // 288: the columns, the column of n, and lanes that only carry loads
 constexpr int ML_GATE_ROWS = 256;
+// threads of a block that owns VC value channels: four a column, the column of n, rounded up to whole warps
+__host__ __device__ constexpr int ml_threads(int vc) { return (4 * (vc + 1) + 31) / 32 * 32; }
 
 __device__ __forceinline__ float ml_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float ml_logsigmoid(float v) { return fminf(v, 0.0f) - log1pf(expf(-fabsf(v))); }
@@ -78,18 +81,32 @@ mlstm_gates_kernel(const float* proj, int ld, int i_off, int f_off, const float*
   if (i == 0) *mx_at = gm[0];
 }
 
-// NP: 16-byte pieces of q (and of k) a thread holds: dim rounded up to 16, over 16.
-template <int NP>
-__global__ void __launch_bounds__(ML_THREADS)
+constexpr int ML_CHUNK = 8;                // rows staged at a time
+
+__device__ __forceinline__ void ml_copy4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ml_copy16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// NP: 16-byte pieces of q (and of k) a thread holds (the state's columns are dp = 16 * ceil(dim / 16) floats long,
+// of which a thread walks 4 * NP >= dp / 4).  ML_VC: value channels a block (the host takes fewer where that fills
+// more of the device).  aligned: every run of values that a row brings starts on a 16-byte boundary and is a
+// multiple of four long.
+// The entry's rows come in chunks of ML_CHUNK: while one chunk is worked on (no barrier between its rows: what a
+// row reads lies in shared memory, what it changes in registers) the next one is on its way (`cp.async`).
+template <int NP, int ML_VC>
+__global__ void __launch_bounds__(ml_threads(ML_VC))
 mlstm_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, const float* gates, float* state,
                   long long slot_stride, long long head_stride, const int* __restrict__ entry_start,
                   const int* __restrict__ entry_slot, int n_head, int dim, int vdim, float q_scale, float* num,
-                  int ld_num, float* den) {
+                  int ld_num, float* den, int ALIGNED, int dp) {
   pdl_trigger();
-  constexpr int DP = 16 * NP;                       // dim rounded up
+  constexpr int ML_THREADS = ml_threads(ML_VC);
+  constexpr int DP = 16 * NP;                       // room for q (and for k) in a staged row
   constexpr int STAGE = 2 * DP + ML_VC + 4;         // q | k | v of the block's channels | the row's three factors
-  constexpr int NL = (STAGE + ML_THREADS - 1) / ML_THREADS;
-  __shared__ __align__(16) float stage[2][STAGE];
+  __shared__ __align__(16) float stage[2][ML_CHUNK][STAGE];
   const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * ML_VC, tid = threadIdx.x;
   const int jc = tid >> 2, r = tid & 3;
   const int t0 = entry_start[e], t1 = entry_start[e + 1];
@@ -97,79 +114,100 @@ mlstm_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, co
   const bool is_n = jc == ML_VC && blockIdx.z == 0;
   const int col = is_n ? vdim : c0 + jc;
   const bool live = is_n || (jc < ML_VC && col < vdim);
-  float* column = state + (size_t)entry_slot[e] * slot_stride + (size_t)h * head_stride + (size_t)col * DP;
-  // what this thread brings in of a row: element idx of the stage
-  auto fetch = [&](int t, float* regs) {
-    const float* p = proj + (size_t)t * ld;
-#pragma unroll
-    for (int l = 0; l < NL; ++l) {
-      const int idx = tid + l * ML_THREADS;
-      float v = 0.0f;
-      if (idx < DP) {
-        if (idx < dim) v = p[q_off + h * dim + idx] * q_scale;
-      } else if (idx < 2 * DP) {
-        if (idx - DP < dim) v = p[k_off + h * dim + idx - DP];
-      } else if (idx < 2 * DP + ML_VC) {
-        const int ch = c0 + idx - 2 * DP;
-        if (ch < vdim) v = p[v_off + h * vdim + ch];
-      } else if (idx < 2 * DP + ML_VC + 3) {
-        v = gates[((size_t)t * n_head + h) * 4 + idx - 2 * DP - ML_VC];
+  float* column = state + (size_t)entry_slot[e] * slot_stride + (size_t)h * head_stride + (size_t)col * dp;
+  const int np = dp / 16;                           // this thread's pieces of a column that exist
+  const int nv = min(ML_VC, vdim - c0);             // value channels of this block
+  float* out_at = num + (size_t)t0 * ld_num + h * vdim + (is_n ? 0 : col);   // this column's numerator of row t0
+  // asks for the rows first .. first + ML_CHUNK - 1 (those below t1) into stage[buf]
+  auto fetch = [&](int first, int buf) {
+    const int rows = min(ML_CHUNK, t1 - first);
+    if (ALIGNED) {
+      const int per = (2 * dim + nv) / 4 + 1;       // 16-byte pieces a row
+      for (int i = tid; i < rows * per; i += ML_THREADS) {
+        const int row = i / per, c = 4 * (i % per);
+        const float* p = proj + (size_t)(first + row) * ld;
+        float* dst = stage[buf][row];
+        if (c < dim) ml_copy16(dst + c, p + q_off + h * dim + c);
+        else if (c < 2 * dim) ml_copy16(dst + DP + c - dim, p + k_off + h * dim + c - dim);
+        else if (c < 2 * dim + nv) ml_copy16(dst + 2 * DP + c - 2 * dim, p + v_off + h * vdim + c0 + c - 2 * dim);
+        else ml_copy16(dst + 2 * DP + ML_VC, gates + ((size_t)(first + row) * n_head + h) * 4);
       }
-      regs[l] = v;
+    } else {
+      const int per = 2 * dim + nv + 3;
+      for (int i = tid; i < rows * per; i += ML_THREADS) {
+        const int row = i / per, c = i % per;
+        const float* p = proj + (size_t)(first + row) * ld;
+        float* dst = stage[buf][row];
+        if (c < dim) ml_copy4(dst + c, p + q_off + h * dim + c);
+        else if (c < 2 * dim) ml_copy4(dst + DP + c - dim, p + k_off + h * dim + c - dim);
+        else if (c < 2 * dim + nv) ml_copy4(dst + 2 * DP + c - 2 * dim, p + v_off + h * vdim + c0 + c - 2 * dim);
+        else ml_copy4(dst + 2 * DP + ML_VC + c - 2 * dim - nv, gates + ((size_t)(first + row) * n_head + h) * 4 + c - 2 * dim - nv);
+      }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  auto put = [&](int buf, const float* regs) {
-#pragma unroll
-    for (int l = 0; l < NL; ++l) {
-      const int idx = tid + l * ML_THREADS;
-      if (idx < STAGE) stage[buf][idx] = regs[l];
-    }
-  };
+  // what no copy writes (q and k beyond dim) stays zero
+  for (int i = tid; i < 2 * ML_CHUNK * STAGE; i += ML_THREADS) (&stage[0][0][0])[i] = 0.0f;
+  __syncthreads();
   pdl_wait();
   if (t0 >= t1) return;
+  fetch(t0, 0);
   float4 S[NP];
 #pragma unroll
   for (int p = 0; p < NP; ++p)
-    S[p] = live ? reinterpret_cast<const float4*>(column)[p * 4 + r] : make_float4(0.f, 0.f, 0.f, 0.f);
-  float regs[NL];
-  fetch(t0, regs);
-  put(0, regs);
-  __syncthreads();
-  for (int t = t0; t < t1; ++t) {
-    const int buf = (t - t0) & 1;
-    if (t + 1 < t1) fetch(t + 1, regs);
-    const float* st = stage[buf];
-    const float keep = st[2 * DP + ML_VC], take = st[2 * DP + ML_VC + 1];
-    const float tv = take * (is_n ? 1.0f : st[2 * DP + (jc < ML_VC ? jc : 0)]);
-    const float4* q4 = reinterpret_cast<const float4*>(st);
-    const float4* k4 = reinterpret_cast<const float4*>(st + DP);
-    float acc = 0.0f;
+    S[p] = live && p < np ? reinterpret_cast<const float4*>(column)[p * 4 + r] : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int first = t0, buf = 0; first < t1; first += ML_CHUNK, buf ^= 1) {
+    if (first + ML_CHUNK < t1) {
+      fetch(first + ML_CHUNK, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();                                // the chunk is there for every thread
+    const int rows = min(ML_CHUNK, t1 - first);
+    // one row: the state's update and the row's numerator (or, in the column of n, its denominator)
+    auto row = [&](int i) {
+      const float* st = stage[buf][i];
+      const float keep = st[2 * DP + ML_VC], take = st[2 * DP + ML_VC + 1];
+      const float tv = take * (is_n ? 1.0f : st[2 * DP + (jc < ML_VC ? jc : 0)]);
+      const float4* q4 = reinterpret_cast<const float4*>(st);
+      const float4* k4 = reinterpret_cast<const float4*>(st + DP);
+      float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);   // four chains, not one of 4 * NP links
 #pragma unroll
-    for (int p = 0; p < NP; ++p) {
-      const float4 q = q4[p * 4 + r], k = k4[p * 4 + r];
-      S[p].x = fmaf(keep, S[p].x, tv * k.x);
-      S[p].y = fmaf(keep, S[p].y, tv * k.y);
-      S[p].z = fmaf(keep, S[p].z, tv * k.z);
-      S[p].w = fmaf(keep, S[p].w, tv * k.w);
-      acc = fmaf(S[p].x, q.x, acc);
-      acc = fmaf(S[p].y, q.y, acc);
-      acc = fmaf(S[p].z, q.z, acc);
-      acc = fmaf(S[p].w, q.w, acc);
+      for (int p = 0; p < NP; ++p) {
+        const float4 q = q4[p * 4 + r], k = k4[p * 4 + r];
+        S[p].x = fmaf(keep, S[p].x, tv * k.x);
+        S[p].y = fmaf(keep, S[p].y, tv * k.y);
+        S[p].z = fmaf(keep, S[p].z, tv * k.z);
+        S[p].w = fmaf(keep, S[p].w, tv * k.w);
+        a4.x = fmaf(S[p].x, q.x, a4.x);
+        a4.y = fmaf(S[p].y, q.y, a4.y);
+        a4.z = fmaf(S[p].z, q.z, a4.z);
+        a4.w = fmaf(S[p].w, q.w, a4.w);
+      }
+      float acc = (a4.x + a4.y) + (a4.z + a4.w);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc *= q_scale;
+      if (r == 0 && live) {
+        if (is_n)
+          den[(size_t)(first + i) * n_head + h] = fmaxf(fabsf(acc), st[2 * DP + ML_VC + 2]) + 1e-6f;
+        else
+          out_at[(size_t)(first + i - t0) * ld_num] = acc;
+      }
+    };
+    if (rows == ML_CHUNK) {     // unrolled: a row's sums and stores overlap the next row's update (a fifth to a third
+#pragma unroll                  // faster than the loop left rolled, measured side by side)
+      for (int i = 0; i < ML_CHUNK; ++i) row(i);
+    } else {
+      for (int i = 0; i < rows; ++i) row(i);
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    if (r == 0 && live) {
-      if (is_n)
-        den[(size_t)t * n_head + h] = fmaxf(fabsf(acc), st[2 * DP + ML_VC + 2]) + 1e-6f;
-      else
-        num[(size_t)t * ld_num + h * vdim + col] = acc;
-    }
-    if (t + 1 < t1) put(buf ^ 1, regs);
-    __syncthreads();
+    __syncthreads();                                // before the chunk after next overwrites this one
   }
   if (live) {
 #pragma unroll
-    for (int p = 0; p < NP; ++p) reinterpret_cast<float4*>(column)[p * 4 + r] = S[p];
+    for (int p = 0; p < NP; ++p)
+      if (p < np) reinterpret_cast<float4*>(column)[p * 4 + r] = S[p];
   }
 }
 
@@ -197,13 +235,33 @@ mlstm_finish_kernel(const float* num, int ld_num, const float* den, const float*
   }
 }
 
-template <int NP>
+template <int NP, int VC>
 static cudaError_t launch_scan(dim3 grid, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off, int v_off,
                                const float* gates, float* state, long long slot_stride, long long head_stride,
                                const int* entry_start, const int* entry_slot, int n_head, int dim, int vdim,
                                float q_scale, float* num, int ld_num, float* den) {
-  return launch_pdl(mlstm_scan_kernel<NP>, grid, dim3(ML_THREADS), 0, stream, proj, ld, q_off, k_off, v_off, gates, state,
-                    slot_stride, head_stride, entry_start, entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den);
+  const int aligned = ((dim | vdim | ld | q_off | k_off | v_off) & 3) == 0 && (((uintptr_t)proj | (uintptr_t)gates) & 15) == 0;
+  grid.z = (vdim + VC - 1) / VC;
+  if (grid.z > 65535) return cudaErrorInvalidValue;
+  return launch_pdl(mlstm_scan_kernel<NP, VC>, grid, dim3(ml_threads(VC)), 0, stream, proj, ld, q_off, k_off, v_off, gates,
+                    state, slot_stride, head_stride, entry_start, entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den,
+                    aligned, (dim + 15) / 16 * 16);
+}
+
+// Fewer value channels a block where 64 would leave most of the device idle (one prompt, a few heads).
+template <int NP>
+static cudaError_t launch_scan_np(int n_entries, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off,
+                                  int v_off, const float* gates, float* state, long long slot_stride,
+                                  long long head_stride, const int* entry_start, const int* entry_slot, int n_head,
+                                  int dim, int vdim, float q_scale, float* num, int ld_num, float* den) {
+  const dim3 grid(n_entries, n_head, 1);
+  const long pairs = (long)n_entries * n_head;
+#define NIB_ML_ARGS grid, stream, proj, ld, q_off, k_off, v_off, gates, state, slot_stride, head_stride, entry_start, \
+                    entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den
+  if (pairs * ((vdim + 63) / 64) >= 120) return launch_scan<NP, 64>(NIB_ML_ARGS);
+  if (pairs * ((vdim + 31) / 32) >= 120) return launch_scan<NP, 32>(NIB_ML_ARGS);
+  return launch_scan<NP, 16>(NIB_ML_ARGS);
+#undef NIB_ML_ARGS
 }
 
 }  // namespace nib
@@ -230,21 +288,20 @@ extern "C" int nib_mlstm(int dtype, const float* proj, int ld, int q_off, int k_
     const long long head_stride = nib_mlstm_state_floats(dim, vdim), slot_stride = head_stride * n_head;
     launch_pdl(mlstm_gates_kernel, dim3(n_entries, n_head), dim3(ML_GATE_ROWS), 0, stream, proj, ld, i_off, f_off, bias_i,
                bias_f, cap, state, slot_stride, head_stride, entry_start, entry_slot, n_head, gates);
-    const dim3 grid(n_entries, n_head, (vdim + ML_VC - 1) / ML_VC);
-    if (grid.z > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
     const float q_scale = 1.0f / sqrtf((float)dim);
     cudaError_t err;
-#define NIB_ML_CASE(NP)                                                                                             \
-  case NP:                                                                                                          \
-    err = launch_scan<NP>(grid, stream, proj, ld, q_off, k_off, v_off, gates, state, slot_stride, head_stride,      \
-                          entry_start, entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den);                   \
-    break;
-    switch ((dim + 15) / 16) {
-      NIB_ML_CASE(1) NIB_ML_CASE(2) NIB_ML_CASE(3) NIB_ML_CASE(4) NIB_ML_CASE(5) NIB_ML_CASE(6) NIB_ML_CASE(7)
-      NIB_ML_CASE(8) NIB_ML_CASE(9) NIB_ML_CASE(10) NIB_ML_CASE(11) NIB_ML_CASE(12) NIB_ML_CASE(13) NIB_ML_CASE(14)
-      NIB_ML_CASE(15) NIB_ML_CASE(16)
-      default: return NIB_ERR_UNSUPPORTED_SIZE;
-    }
+#define NIB_ML_CASE(NP)                                                                                                \
+  err = launch_scan_np<NP>(n_entries, stream, proj, ld, q_off, k_off, v_off, gates, state, slot_stride, head_stride,   \
+                           entry_start, entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den)
+    const int pieces = (dim + 15) / 16;     // a thread's pieces: the next size that is built
+    if (pieces <= 1) NIB_ML_CASE(1);
+    else if (pieces <= 2) NIB_ML_CASE(2);
+    else if (pieces <= 3) NIB_ML_CASE(3);
+    else if (pieces <= 4) NIB_ML_CASE(4);
+    else if (pieces <= 6) NIB_ML_CASE(6);
+    else if (pieces <= 8) NIB_ML_CASE(8);
+    else if (pieces <= 12) NIB_ML_CASE(12);
+    else NIB_ML_CASE(16);
 #undef NIB_ML_CASE
     if (err != cudaSuccess) return (int)err;
   }
