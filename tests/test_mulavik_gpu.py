@@ -180,7 +180,8 @@ def _sink_attention(q, k, v, scale, pos0, sink):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("hd,n_head,n_kv_head", [(64, 4, 2), (32, 2, 2), (48, 3, 1), (128, 2, 1), (24, 2, 1)])
+@pytest.mark.parametrize("hd,n_head,n_kv_head", [(64, 4, 2), (32, 2, 2), (48, 3, 1), (128, 2, 1), (24, 2, 1), (96, 2, 2),
+                                                 (160, 2, 1)])
 def test_every_attention_kernel_with_the_sink(hd, n_head, n_kv_head, dtype):
     """Portions and single tokens side by side through the dispatcher (which picks the tcgen05, the warp-MMA or the
     general kernel for portions and the MMA or the streaming kernel for single tokens), with and without the
