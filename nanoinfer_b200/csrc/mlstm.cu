@@ -15,8 +15,9 @@
 //   mlstm_scan   : a block per (entry, head, 64 value channels) walks the entry's rows in order.  A column of S
 //                  belongs to one value channel and the columns do not see one another; n is one more column whose
 //                  value is 1 (the first block of a head carries it).  A column lives in the registers of four
-//                  neighbouring threads, which take the 16-byte pieces r, r + 4, r + 8, ... of q and k (the four
-//                  read 64 bytes side by side: no bank conflicts; S^T q is a sum over four lanes, two shuffles).  The
+//                  (columns of more than 96 floats: eight) neighbouring threads, which take the 16-byte pieces r,
+//                  r + R, r + 2R, ... of q and k (they read side by side: no bank conflicts; S^T q is a sum over
+//                  those lanes, two or three shuffles).  The
 //                  rows' q, k, v and factors come into shared memory eight rows at a time by `cp.async`, the next
 //                  eight while these are worked on: two barriers per eight rows, none between rows.
 //                  It leaves the numerators S'^T q and the denominators.
@@ -31,8 +32,8 @@
 namespace nib {
 
 constexpr int ML_GATE_ROWS = 256;
-// threads of a block that owns VC value channels: four a column, the column of n, rounded up to whole warps
-__host__ __device__ constexpr int ml_threads(int vc) { return (4 * (vc + 1) + 31) / 32 * 32; }
+// threads of a block that owns VC value channels: R a column, the column of n, rounded up to whole warps
+__host__ __device__ constexpr int ml_threads(int vc, int r) { return (r * (vc + 1) + 31) / 32 * 32; }
 
 __device__ __forceinline__ float ml_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float ml_logsigmoid(float v) { return fminf(v, 0.0f) - log1pf(expf(-fabsf(v))); }
@@ -90,32 +91,33 @@ __device__ __forceinline__ void ml_copy16(float* dst, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-// NP: 16-byte pieces of q (and of k) a thread holds (the state's columns are dp = 16 * ceil(dim / 16) floats long,
-// of which a thread walks 4 * NP >= dp / 4).  ML_VC: value channels a block (the host takes fewer where that fills
-// more of the device).  aligned: every run of values that a row brings starts on a 16-byte boundary and is a
-// multiple of four long.
+// R: threads a column (4 for columns of up to 96 floats, 8 beyond: a row's time grows with the pieces a thread
+// walks, and more lanes a column cost a shuffle more).  NP: 16-byte pieces of q (and of k) a thread
+// holds: it walks the pieces r, r + R, r + 2R, ... of a column of dp = 16 * ceil(dim / 16) floats, R * NP >= dp / 4.
+// ML_VC: value channels a block (the host takes fewer where that fills more of the device).  aligned: every run of
+// values that a row brings starts on a 16-byte boundary and is a multiple of four long.
 // The entry's rows come in chunks of ML_CHUNK: while one chunk is worked on (no barrier between its rows: what a
 // row reads lies in shared memory, what it changes in registers) the next one is on its way (`cp.async`).
-template <int NP, int ML_VC>
-__global__ void __launch_bounds__(ml_threads(ML_VC))
+template <int NP, int R, int ML_VC>
+__global__ void __launch_bounds__(ml_threads(ML_VC, R))
 mlstm_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, const float* gates, float* state,
                   long long slot_stride, long long head_stride, const int* __restrict__ entry_start,
                   const int* __restrict__ entry_slot, int n_head, int dim, int vdim, float q_scale, float* num,
                   int ld_num, float* den, int ALIGNED, int dp) {
   pdl_trigger();
-  constexpr int ML_THREADS = ml_threads(ML_VC);
-  constexpr int DP = 16 * NP;                       // room for q (and for k) in a staged row
+  constexpr int ML_THREADS = ml_threads(ML_VC, R);
+  constexpr int DP = 4 * R * NP;                    // room for q (and for k) in a staged row
   constexpr int STAGE = 2 * DP + ML_VC + 4;         // q | k | v of the block's channels | the row's three factors
   __shared__ __align__(16) float stage[2][ML_CHUNK][STAGE];
   const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * ML_VC, tid = threadIdx.x;
-  const int jc = tid >> 2, r = tid & 3;
+  const int jc = tid / R, r = tid % R;
   const int t0 = entry_start[e], t1 = entry_start[e + 1];
   // this thread's column: a value channel of the block, or (first block of the head) the column of n
   const bool is_n = jc == ML_VC && blockIdx.z == 0;
   const int col = is_n ? vdim : c0 + jc;
   const bool live = is_n || (jc < ML_VC && col < vdim);
   float* column = state + (size_t)entry_slot[e] * slot_stride + (size_t)h * head_stride + (size_t)col * dp;
-  const int np = dp / 16;                           // this thread's pieces of a column that exist
+  const int n4 = dp / 4;                            // 16-byte pieces of a column: this thread's are r + p * R < n4
   const int nv = min(ML_VC, vdim - c0);             // value channels of this block
   float* out_at = num + (size_t)t0 * ld_num + h * vdim + (is_n ? 0 : col);   // this column's numerator of row t0
   // asks for the rows first .. first + ML_CHUNK - 1 (those below t1) into stage[buf]
@@ -155,7 +157,7 @@ mlstm_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, co
   float4 S[NP];
 #pragma unroll
   for (int p = 0; p < NP; ++p)
-    S[p] = live && p < np ? reinterpret_cast<const float4*>(column)[p * 4 + r] : make_float4(0.f, 0.f, 0.f, 0.f);
+    S[p] = live && p * R + r < n4 ? reinterpret_cast<const float4*>(column)[p * R + r] : make_float4(0.f, 0.f, 0.f, 0.f);
   for (int first = t0, buf = 0; first < t1; first += ML_CHUNK, buf ^= 1) {
     if (first + ML_CHUNK < t1) {
       fetch(first + ML_CHUNK, buf ^ 1);
@@ -175,7 +177,7 @@ mlstm_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, co
       float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);   // four chains, not one of 4 * NP links
 #pragma unroll
       for (int p = 0; p < NP; ++p) {
-        const float4 q = q4[p * 4 + r], k = k4[p * 4 + r];
+        const float4 q = q4[p * R + r], k = k4[p * R + r];
         S[p].x = fmaf(keep, S[p].x, tv * k.x);
         S[p].y = fmaf(keep, S[p].y, tv * k.y);
         S[p].z = fmaf(keep, S[p].z, tv * k.z);
@@ -187,7 +189,8 @@ mlstm_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, co
       }
       float acc = (a4.x + a4.y) + (a4.z + a4.w);
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      if (R >= 4) acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      if (R >= 8) acc += __shfl_xor_sync(0xffffffffu, acc, 4);
       acc *= q_scale;
       if (r == 0 && live) {
         if (is_n)
@@ -207,7 +210,7 @@ mlstm_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, co
   if (live) {
 #pragma unroll
     for (int p = 0; p < NP; ++p)
-      if (p < np) reinterpret_cast<float4*>(column)[p * 4 + r] = S[p];
+      if (p * R + r < n4) reinterpret_cast<float4*>(column)[p * R + r] = S[p];
   }
 }
 
@@ -235,7 +238,7 @@ mlstm_finish_kernel(const float* num, int ld_num, const float* den, const float*
   }
 }
 
-template <int NP, int VC>
+template <int NP, int R, int VC>
 static cudaError_t launch_scan(dim3 grid, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off, int v_off,
                                const float* gates, float* state, long long slot_stride, long long head_stride,
                                const int* entry_start, const int* entry_slot, int n_head, int dim, int vdim,
@@ -243,13 +246,13 @@ static cudaError_t launch_scan(dim3 grid, cudaStream_t stream, const float* proj
   const int aligned = ((dim | vdim | ld | q_off | k_off | v_off) & 3) == 0 && (((uintptr_t)proj | (uintptr_t)gates) & 15) == 0;
   grid.z = (vdim + VC - 1) / VC;
   if (grid.z > 65535) return cudaErrorInvalidValue;
-  return launch_pdl(mlstm_scan_kernel<NP, VC>, grid, dim3(ml_threads(VC)), 0, stream, proj, ld, q_off, k_off, v_off, gates,
+  return launch_pdl(mlstm_scan_kernel<NP, R, VC>, grid, dim3(ml_threads(VC, R)), 0, stream, proj, ld, q_off, k_off, v_off, gates,
                     state, slot_stride, head_stride, entry_start, entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den,
                     aligned, (dim + 15) / 16 * 16);
 }
 
 // Fewer value channels a block where 64 would leave most of the device idle (one prompt, a few heads).
-template <int NP>
+template <int NP, int R>
 static cudaError_t launch_scan_np(int n_entries, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off,
                                   int v_off, const float* gates, float* state, long long slot_stride,
                                   long long head_stride, const int* entry_start, const int* entry_slot, int n_head,
@@ -258,9 +261,9 @@ static cudaError_t launch_scan_np(int n_entries, cudaStream_t stream, const floa
   const long pairs = (long)n_entries * n_head;
 #define NIB_ML_ARGS grid, stream, proj, ld, q_off, k_off, v_off, gates, state, slot_stride, head_stride, entry_start, \
                     entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den
-  if (pairs * ((vdim + 63) / 64) >= 120) return launch_scan<NP, 64>(NIB_ML_ARGS);
-  if (pairs * ((vdim + 31) / 32) >= 120) return launch_scan<NP, 32>(NIB_ML_ARGS);
-  return launch_scan<NP, 16>(NIB_ML_ARGS);
+  if (pairs * ((vdim + 63) / 64) >= 120) return launch_scan<NP, R, 64>(NIB_ML_ARGS);
+  if (pairs * ((vdim + 31) / 32) >= 120) return launch_scan<NP, R, 32>(NIB_ML_ARGS);
+  return launch_scan<NP, R, 16>(NIB_ML_ARGS);
 #undef NIB_ML_ARGS
 }
 
@@ -290,18 +293,20 @@ extern "C" int nib_mlstm(int dtype, const float* proj, int ld, int q_off, int k_
                bias_f, cap, state, slot_stride, head_stride, entry_start, entry_slot, n_head, gates);
     const float q_scale = 1.0f / sqrtf((float)dim);
     cudaError_t err;
-#define NIB_ML_CASE(NP)                                                                                                \
-  err = launch_scan_np<NP>(n_entries, stream, proj, ld, q_off, k_off, v_off, gates, state, slot_stride, head_stride,   \
-                           entry_start, entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den)
-    const int pieces = (dim + 15) / 16;     // a thread's pieces: the next size that is built
-    if (pieces <= 1) NIB_ML_CASE(1);
-    else if (pieces <= 2) NIB_ML_CASE(2);
-    else if (pieces <= 3) NIB_ML_CASE(3);
-    else if (pieces <= 4) NIB_ML_CASE(4);
-    else if (pieces <= 6) NIB_ML_CASE(6);
-    else if (pieces <= 8) NIB_ML_CASE(8);
-    else if (pieces <= 12) NIB_ML_CASE(12);
-    else NIB_ML_CASE(16);
+#define NIB_ML_CASE(NP, R)                                                                                             \
+  err = launch_scan_np<NP, R>(n_entries, stream, proj, ld, q_off, k_off, v_off, gates, state, slot_stride, head_stride, \
+                              entry_start, entry_slot, n_head, dim, vdim, q_scale, num, ld_num, den)
+    const int pieces = (dim + 15) / 16 * 4;   // 16-byte pieces of a column; a thread's share: the next size that is built
+    // (measured at 952 rows: columns of 96 floats 0.39 ms with four threads a column, 0.41 with eight, 0.51 with two;
+    // columns of 256 floats 0.91 to 1.2 ms with four, 0.79 with eight)
+    if (pieces <= 4) NIB_ML_CASE(1, 4);
+    else if (pieces <= 8) NIB_ML_CASE(2, 4);
+    else if (pieces <= 12) NIB_ML_CASE(3, 4);
+    else if (pieces <= 16) NIB_ML_CASE(4, 4);
+    else if (pieces <= 24) NIB_ML_CASE(6, 4);
+    else if (pieces <= 32) NIB_ML_CASE(4, 8);
+    else if (pieces <= 48) NIB_ML_CASE(6, 8);
+    else NIB_ML_CASE(8, 8);
 #undef NIB_ML_CASE
     if (err != cudaSuccess) return (int)err;
   }
