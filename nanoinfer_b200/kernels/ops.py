@@ -798,9 +798,9 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, b
 def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
               n_head: int, scale: float, window: int, plan, sink: bool = False) -> None:
     """Causal attention of the step's rows over one cache layer.  ``sink``: the softmax's denominator has
-    one more term, exp(0) (a key of score 0 that has no value; every kernel adds it where it divides).  ``ctx`` is the step's StepContext,
-    ``plan`` says which rows are single decoded tokens and how the prompt portions are cut into
-    tiles (``parts.attention.AttentionPlan``).  Single decoded tokens go to the split-KV kernel;
+    one more term, exp(0) (a key of score 0 that has no value; every kernel adds it where it divides).
+    ``ctx`` is the step's StepContext, ``plan`` says which rows are single decoded tokens and how the
+    prompt portions are cut into tiles (``parts.attention.AttentionPlan``).  Single decoded tokens go to the split-KV kernel;
     prompt portions go to the tiled tensor-core kernels in bfloat16 (head sizes 16..128 in steps of
     16) and to the general kernel otherwise."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
